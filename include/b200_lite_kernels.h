@@ -335,18 +335,22 @@ int b2l_rope_heads(void* dst, int64_t dst_row_stride, int dst_head_stride, const
                    int src_head_stride, const void* cos_sin_f32, int64_t tokens, int heads, int width, int rot_dims,
                    int dtype, void* stream);
 
-/* Short causal convolution per channel + SiLU over a ragged step, and the slot's tail (last taps-1 inputs) update.
+/* Short causal convolution per channel + SiLU (activation 1; 0 = none) over a ragged step, and the slot's tail (last
+ * taps-1 inputs) update.
  * in: [tokens, >= channels] with row stride; weight [channels, taps] (last column = current token); tail
  * [slots, taps - 1, channels] in dtype. */
 int b2l_causal_conv_silu(void* out, const void* in, int64_t in_row_stride, const void* weight, const void* bias,
                          void* tail, const void* seq_start, const void* seq_ctx, const void* seq_slot, int64_t num_seqs,
-                         int64_t tokens, int channels, int taps, int dtype, void* stream);
+                         int64_t tokens, int channels, int taps, int activation, int dtype, void* stream);
 /* Scalar-decay state-space recurrence (csrc/ssm_scan.cu).  xbc rows = [x: heads*head_dim | B: groups*state | C: ...];
- * state_f32 [slots, heads, state, head_dim] fp32; y_f32 [tokens, heads*head_dim] fp32. */
+ * state_f32 [slots, heads, state, head_dim] fp32; y_f32 [tokens, heads*head_dim] fp32.  fixed_decay_f32 [heads]
+ * (nullable): decayed linear attention S <- decay_h S + B x^T, y = S^T C with dt = 1 and no skip term (dt_raw, dt_bias,
+ * a_log, d_skip unused); silu_inputs: SiLU on x, B and C as they are read. */
 int b2l_ssm_scan(void* y_f32, void* state_f32, const void* xbc, int64_t xbc_row_stride, const void* dt_raw,
                  int64_t dt_row_stride, const void* dt_bias, const void* a_log, const void* d_skip,
                  const void* seq_start, const void* seq_ctx, const void* seq_slot, int64_t num_seqs, int heads,
-                 int groups, int state_size, int head_dim, int dtype, void* stream);
+                 int groups, int state_size, int head_dim, const void* fixed_decay_f32, int silu_inputs, int dtype,
+                 void* stream);
 /* out = unit_rms(y * silu(z)) * weight, the unit RMS taken in `groups` equal parts of the row. */
 int b2l_gated_group_norm(void* out, const void* y_f32, const void* z, int64_t z_row_stride, const void* weight,
                          int64_t rows, int inner, int groups, float eps, int dtype, void* stream);
@@ -362,15 +366,60 @@ int b2l_attn_prepare(void* qkv, int64_t qkv_row_stride, void* kv_pool, int64_t k
 /* Soft-capped attention with an optional per-head sink over the pool (csrc/attention_sink.cu).  num_splits == 0: tiled
  * mode for sequences of up to max_q_len new tokens; num_splits > 0: every listed sequence brings one token, its keys
  * (from the first one it sees) are cut into num_splits ranges of split_keys and merged (workspace:
- * b2l_sink_attention_workspace_bytes).  window > 0: token p sees keys p - window + 1 .. p only.  v_col0 < 0: a pool
+ * b2l_sink_attention_workspace_bytes).  window > 0: token p sees keys p - window + 1 .. p only; block > 0 (window <= 0):
+ * token p sees keys floor(p / block) * block .. p only.  v_col0 < 0: a pool
  * row is [keys | values]; v_col0 >= 0: the values start at that column (0: they are the keys' leading columns). */
 int64_t b2l_sink_attention_workspace_bytes(int64_t num_seqs, int heads, int v_head_dim, int num_splits);
 int b2l_sink_attention(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride, const void* kv_pool,
                        int64_t kv_row_stride, const void* table_i32, int64_t table_row_stride, const void* seq_start,
                        const void* seq_ctx, const void* seq_slot, const void* seq_list, int64_t num_seqs,
                        int max_q_len, const void* sink, int heads, int kv_heads, int head_dim, int v_head_dim,
-                       float scale, float softcap, int window, int v_col0, int num_splits, int split_keys,
+                       float scale, float softcap, int window, int block, int v_col0, int num_splits, int split_keys,
                        void* workspace, int64_t workspace_bytes, int dtype, void* stream);
+
+/* Parallel-block layer-list models with a depth-weighted residual stack (csrc/parallel_stream.cu).
+ * embed_rmsnorm: residual_f32[t] = unit_rms(scale * embed[token[t]]) * (weight_offset + weight) (weight nullable).
+ * depth_mix_norms: x = sum_j coef[j] * stack[j] over `count` levels `level_stride` floats apart (coef NULL: x = the last
+ * level), written to x_out_f32 (nullable when n % 4 == 0 and n <= 8192), h1 = unit_rms(x) * (offset + w1), h2 likewise
+ * (both nullable).  branch_sum_residual: residual += scale * (a' + b') + c with a' = unit_rms(a) * a_weight when the
+ * weight is given, else a (b likewise; b, c nullable); act (nullable) = the new residual in dtype.
+ * gelu_mul_gather: out[t, d] = gelu_tanh(z[t, d]) * table[token[t], col0 + d], d < dim. */
+int b2l_embed_rmsnorm(void* residual_f32, const void* tokens_i32, const void* embed, const void* weight, int64_t rows,
+                      int64_t n, int64_t vocab, float eps, float weight_offset, float scale, int dtype, void* stream);
+int b2l_depth_mix_norms(void* x_out_f32, void* h1, void* h2, const void* stack_f32, int64_t level_stride,
+                        const void* coef, int count, const void* w1, const void* w2, int64_t rows, int64_t n, float eps,
+                        float weight_offset, int dtype, void* stream);
+int b2l_branch_sum_residual(void* residual_f32, void* act, const void* a, int64_t a_row_stride, const void* a_weight,
+                            const void* b, int64_t b_row_stride, const void* b_weight, const void* c,
+                            int64_t c_row_stride, int64_t rows, int64_t n, float eps, float scale, int dtype,
+                            void* stream);
+int b2l_gelu_mul_gather(void* out, const void* z, int64_t z_row_stride, const void* tokens_i32, const void* table,
+                        int64_t table_row_stride, int64_t vocab, int col0, int dim, int64_t rows, int dtype,
+                        void* stream);
+
+/* Element-wise gated recurrences S_t = a_t S_(t-1) + b_t, o_t = S_t g_t over a ragged step (csrc/gated_recurrence.cu).
+ * mode 0 (minimal GRU): p0 / p1 / p2 = update-gate, candidate, output-gate pre-activations.  mode 1 (real-gated LRU):
+ * p0 = recurrence input, p1 / p2 = recurrence- / input-gate pre-activations (+ bias_r / bias_i), p3 = pre-activation
+ * of the gelu branch, a = exp(-decay_scale * r * softplus(lam)).  state_f32 [slots, width]. */
+int b2l_gated_scan(void* out, int64_t out_row_stride, void* state_f32, const void* p0, int64_t p0_row_stride,
+                   const void* p1, int64_t p1_row_stride, const void* p2, int64_t p2_row_stride, const void* p3,
+                   int64_t p3_row_stride, const void* bias_r, const void* bias_i, const void* lam, float decay_scale,
+                   const void* seq_start, const void* seq_ctx, const void* seq_slot, int64_t num_seqs, int width,
+                   int mode, int dtype, void* stream);
+/* out = unit_rms(y_f32) * weight * sigmoid(z) over whole rows of n. */
+int b2l_norm_sigmoid_gate(void* out, const void* y_f32, const void* z, int64_t z_row_stride, const void* weight,
+                          int64_t rows, int n, float eps, int dtype, void* stream);
+
+/* Rotary table from given per-pair frequencies (csrc/rotary_heads.cu): cos_sin_f32[t] = magnitude * [cos(pos f_i) |
+ * sin(pos f_i)], fp32 angles.  head_norm_rope_prepare: per token of a fused [q | k | v] row, per-head RMS norm of q and
+ * k with one [head_dim] weight each (nullable), rotation of the first rot_dims entries (pairing 0: neighbours 2i, 2i+1;
+ * 1: i and i + rot_dims / 2), q in place, k and v into pool row kv_rows[t]. */
+int b2l_rope_table_freqs(void* cos_sin_f32, const void* pos_i32, const void* freqs_f32, int64_t tokens, int rot_dims,
+                         float magnitude, void* stream);
+int b2l_head_norm_rope_prepare(void* qkv, int64_t qkv_row_stride, void* kv_pool, int64_t kv_row_stride,
+                               const void* kv_rows_i32, const void* cos_sin_f32, const void* q_norm_weight,
+                               const void* k_norm_weight, int64_t tokens, int heads, int kv_heads, int head_dim,
+                               int v_head_dim, int rot_dims, int pairing, float eps, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

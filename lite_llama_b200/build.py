@@ -66,10 +66,11 @@ def _compile(src: Path, force: bool) -> Path:
 # plumbing every subset needs (error strings, launch counter, TMA descriptors)
 BASE_SOURCES = ("core", "tma_desc")
 # what the layer-list decoders launch between them: dense tcgen05 GEMM, fp32 / odd-shape / per-head / grouped GEMM,
-# residual stream, state-space, attention and latent-attention kernels, expert routing, argmax and expert sum.  Each
+# residual streams (sequential and parallel blocks), state-space and gated recurrences, attention, rotary and
+# latent-attention kernels, expert routing, argmax and expert sum.  Each
 # registered architecture names its own subset (executor.registry.Architecture.sources).
-LAYERED_SOURCES = ("gemm_dense", "gemm_simt", "gemm_rows_mma", "residual_stream", "ssm_scan", "attention_sink",
-                   "latent_attention", "moe_routing", "elementwise")
+LAYERED_SOURCES = ("gemm_dense", "gemm_simt", "gemm_rows_mma", "residual_stream", "parallel_stream", "ssm_scan",
+                   "gated_recurrence", "attention_sink", "rotary_heads", "latent_attention", "moe_routing", "elementwise")
 LINK_STAMP = OBJ_DIR / "link.stamp"
 
 

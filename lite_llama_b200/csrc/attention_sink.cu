@@ -4,7 +4,8 @@
 // K and V rows may have different head sizes (D, Dv): a pool row is [G*D keys | G*Dv values]; the values may instead
 // start at any column `v_col0` of the row (v_col0 = 0: the values ARE the leading Dv columns of the keys, which is
 // how a latent cache [latent | rotated key part] is read by queries that were multiplied into the latent space).
-// A sliding window (`window` > 0) limits token p to the keys p - window + 1 .. p.
+// A sliding window (`window` > 0) limits token p to the keys p - window + 1 .. p; a block-diagonal mask (`block` > 0)
+// to the keys of its own run of `block` positions, floor(p / block) * block .. p (runs are counted from position 0).
 //
 //   attn_prepare   per token: whole-row RMS norm of q and of k (one statistic over ALL heads, plain weight),
 //                  position-dependent query gain, value mixing with an earlier layer's values, K|V cache write
@@ -39,10 +40,17 @@ struct AttnArgs {
   float* part;
   int H, G, D, Dv, PH, BQ, nsplit, chunk;
   int window, v_col0;          // window <= 0: every earlier key is visible; v_col0: first value column of a pool row
+  int block;                   // > 0 (and no window): block-diagonal mask, see first_visible
   int head_rows;               // tensor-core kernel, one new token per sequence: the tile's rows are the query HEADS of
                                // one kv head (not tokens), blockIdx.x is a key range, results go to `part`
   float scale, softcap;
 };
+
+// first key position the token at `pos` sees (may be negative under a window: callers clamp where they index);
+// non-decreasing in pos for every mask kind, which the tile-level bounds below rely on
+__device__ __forceinline__ int first_visible(const AttnArgs& a, int pos) {
+  return a.window > 0 ? pos - a.window + 1 : (a.block > 0 ? pos - pos % a.block : 0);
+}
 
 // ---- tiled mode on the CUDA cores (fp32 activations, or head sizes the tensor-core tiles do not take) ------------
 template <typename T, int DVJ>
@@ -63,7 +71,7 @@ __global__ void __launch_bounds__(kWarps * 32) sink_attention_kernel(AttnArgs a)
   if (t0 >= qlen) return;
   const int t_count = min(a.BQ, qlen - t0);
   const int key_hi = ctx + t0 + t_count;                // exclusive
-  const int key_lo = a.window > 0 ? max(0, ctx + t0 - a.window + 1) : 0;      // first key the tile's first token sees
+  const int key_lo = max(0, first_visible(a, ctx + t0));                      // first key the tile's first token sees
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const T* q = (const T*)a.q;
   const T* kv = (const T*)a.kv;
@@ -111,7 +119,7 @@ __global__ void __launch_bounds__(kWarps * 32) sink_attention_kernel(AttnArgs a)
 #pragma unroll
     for (int i = 0; i < kRowsPerWarp; ++i) {
       if (row_pos[i] < k0) continue;              // warp-uniform: nothing visible in this tile (or unused row)
-      const int row_lo = a.window > 0 ? row_pos[i] - a.window + 1 : 0;
+      const int row_lo = first_visible(a, row_pos[i]);
       if (row_lo >= k0 + nk) continue;            // warp-uniform: the row's window starts after this tile
       float sv = sc[i] * a.scale;
       if (a.softcap > 0.f) sv = a.softcap * tanhf(sv * inv_cap);
@@ -206,16 +214,16 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
   const int t_count = hr ? min(kTileM, g * per + per - h_base) : min(kTileM, qlen - t0);       // live rows
   const int h = h_base;
   const int64_t slot = a.seq_slot[s];
-  const int win_lo = a.window > 0 ? max(0, ctx - a.window + 1) : 0;            // head rows: the token's first visible key
+  const int win_lo = max(0, first_visible(a, ctx));                            // head rows: the token's first visible key
   const int range_lo = hr ? win_lo + blockIdx.x * a.chunk : 0;
   const int key_hi = hr ? min(range_lo + a.chunk, ctx + 1) : ctx + t0 + t_count;               // exclusive
   const bool ok0 = r0 < t_count, ok1 = r1 < t_count;
   const int pos0 = hr ? key_hi - 1 : ctx + t0 + r0, pos1 = hr ? key_hi - 1 : ctx + t0 + r1;     // last visible key of each row
-  const int lo0 = hr ? range_lo : (a.window > 0 ? pos0 - a.window + 1 : 0);                     // first one
-  const int lo1 = hr ? range_lo : (a.window > 0 ? pos1 - a.window + 1 : 0);
+  const int lo0 = hr ? range_lo : first_visible(a, pos0);                                       // first one
+  const int lo1 = hr ? range_lo : first_visible(a, pos1);
   // first key tile: the one that holds the first key of the tile's first row (tiles stay aligned to kTileN)
-  const int k_first = hr ? range_lo / kTileN * kTileN : (a.window > 0 ? max(0, ctx + t0 - a.window + 1) / kTileN * kTileN : 0);
-  const int warp_first = hr ? range_lo : (a.window > 0 ? ctx + t0 + warp * 16 - a.window + 1 : 0);   // first key of the warp's rows
+  const int k_first = hr ? range_lo / kTileN * kTileN : max(0, first_visible(a, ctx + t0)) / kTileN * kTileN;
+  const int warp_first = hr ? range_lo : first_visible(a, ctx + t0 + warp * 16);                    // first key of the warp's rows
   const T* q = (const T*)a.q;
   const T* kv = (const T*)a.kv;
   uint32_t qf[DP / 16][4];
@@ -475,7 +483,7 @@ __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
   const int hchunks = (per + kSplitRows - 1) / kSplitRows;
   const int g = blockIdx.y / hchunks, h_first = g * per + (blockIdx.y % hchunks) * kSplitRows;
   const int h_count = min(kSplitRows, g * per + per - h_first);
-  const int win_lo = a.window > 0 ? max(0, ctx - a.window + 1) : 0;          // the new token's first visible key
+  const int win_lo = max(0, first_visible(a, ctx));                          // the new token's first visible key
   const int key_lo = win_lo + blockIdx.x * a.chunk, key_hi = min(key_lo + a.chunk, ctx + 1);
   const T* q = (const T*)a.q;
   const T* kv = (const T*)a.kv;
@@ -900,14 +908,14 @@ extern "C" int64_t b2l_sink_attention_workspace_bytes(int64_t num_seqs, int head
 /* num_splits == 0: tiled mode over `max_q_len`-token sequences; > 0: split mode, every listed sequence brings ONE token
  * and `split_keys` keys go to each of the num_splits ranges, counted from the token's first visible key
  * (num_splits * split_keys >= the most keys any listed token sees: context + 1, or the window if that is smaller).
- * window <= 0: no sliding window; v_col0 < 0: the values follow the keys in a pool row (column kv_heads * head_dim). */
+ * window <= 0: no sliding window; block > 0 (window <= 0): block-diagonal mask; v_col0 < 0: the values follow the keys in a pool row (column kv_heads * head_dim). */
 extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride,
                                   const void* kv_pool, int64_t kv_row_stride, const void* table_i32,
                                   int64_t table_row_stride, const void* seq_start, const void* seq_ctx,
                                   const void* seq_slot, const void* seq_list, int64_t num_seqs, int max_q_len,
                                   const void* sink, int heads, int kv_heads, int head_dim, int v_head_dim, float scale,
-                                  float softcap, int window, int v_col0, int num_splits, int split_keys,
-                                  void* workspace, int64_t workspace_bytes, int dtype, void* stream) {
+                                  float softcap, int window, int block, int v_col0, int num_splits,
+                                  int split_keys, void* workspace, int64_t workspace_bytes, int dtype, void* stream) {
   B2L_REQUIRE(out && q && kv_pool && table_i32 && seq_start && seq_ctx && seq_slot, "sink_attention: null pointer");
   B2L_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "sink_attention: %d heads must be a multiple of num_kv_heads %d",
               heads, kv_heads);
@@ -926,6 +934,7 @@ extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void*
   a.BQ = kRows / a.PH;
   a.nsplit = num_splits; a.chunk = split_keys; a.scale = scale; a.softcap = softcap;
   a.window = window > 0 ? window : 0;
+  a.block = (window <= 0 && block > 0) ? block : 0;
   a.v_col0 = v_col0 >= 0 ? v_col0 : kv_heads * head_dim;
   a.head_rows = 0;
   const int hchunks = (per + a.PH - 1) / a.PH;

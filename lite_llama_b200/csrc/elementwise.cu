@@ -491,6 +491,10 @@ extern "C" int b2l_swiglu(void* c, const void* a, const void* b, int64_t rows, i
     b2l_launch(swiglu_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), (size_t)(0), st, (__nv_bfloat16*)c, (const __nv_bfloat16*)a,
                                                           (const __nv_bfloat16*)b, rows, n, a_row_stride, b_row_stride,
                                                           c_row_stride, vec);
+  else if (dtype == B2L_F32)            // true 32-bit rows of the layer-list models: the scalar path
+    b2l_launch(swiglu_kernel<float>, dim3((unsigned)(cdiv64(n, threads) > 64 ? 64 : cdiv64(n, threads)), gy), dim3(threads),
+               (size_t)(0), st, (float*)c, (const float*)a, (const float*)b, rows, n, a_row_stride, b_row_stride,
+               c_row_stride, 0);
   else
     B2L_UNSUPPORTED("swiglu: dtype %d", dtype);
   B2L_LAUNCH_CHECK();

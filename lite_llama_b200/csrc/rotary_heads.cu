@@ -1,0 +1,117 @@
+// Rotary positions with per-pair frequencies given as a table (frequency-interpolated variants compute the table on
+// the host), and the per-token preparation of attention layers that norm each head on its own:
+//   * rope_table_freqs         cos_sin[t] = [mag * cos(pos[t] * f_i), i < rot_dims / 2 | mag * sin(pos[t] * f_i)],
+//                              the angle is the fp32 product of the position and the fp32 frequency
+//   * head_norm_rope_prepare   per token of a fused [q | k | v] projection row: every q head and every k head is
+//                              RMS-normed over its own head_dim entries with ONE weight [head_dim] shared by the heads
+//                              (nullable = no norm), then its first rot_dims entries are rotated (pairing 0: entries
+//                              2i and 2i+1; pairing 1: entries i and i + rot_dims / 2); q is updated in place, k and v
+//                              go to pool row kv_rows[t] = [k heads | v heads].
+// Statistics, angles and the rotation are fp32; one rounding to T at the end.
+#include "common.cuh"
+
+namespace {
+
+__global__ void rope_table_freqs_kernel(float* __restrict__ out, const int* __restrict__ pos,
+                                        const float* __restrict__ freqs, int64_t total, int half, float mag) {
+  pdl_prologue();
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / half;
+    const int i = (int)(idx - t * half);
+    const float a = (float)pos[t] * freqs[i];
+    float sn, cs;
+    sincosf(a, &sn, &cs);
+    out[t * 2 * half + i] = cs * mag;
+    out[t * 2 * half + half + i] = sn * mag;
+  }
+}
+
+constexpr int kPrepWarps = 4;
+
+// One CTA per token, one warp per head at a time.  A head is staged (normed, fp32) in the warp's shared-memory row so
+// that either pairing finds its partner there.
+template <typename T>
+__global__ void __launch_bounds__(kPrepWarps * 32) head_norm_rope_prepare_kernel(
+    T* __restrict__ qkv, int64_t qkv_stride, T* __restrict__ pool, int64_t pool_stride, const int* __restrict__ kv_rows,
+    const float* __restrict__ cos_sin, const T* __restrict__ q_w, const T* __restrict__ k_w, int H, int G, int D,
+    int Dv, int rot_dims, int pairing, float eps) {
+  pdl_prologue();
+  extern __shared__ float stage[];                 // [kPrepWarps][D]
+  const int64_t t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* row = stage + warp * D;
+  T* src = qkv + t * qkv_stride;
+  T* dst_pool = pool + (int64_t)kv_rows[t] * pool_stride;
+  const int half = rot_dims / 2;
+  const float* cs = cos_sin ? cos_sin + t * rot_dims : nullptr;
+  for (int h = warp; h < H + G; h += kPrepWarps) {
+    const bool is_q = h < H;
+    const T* in = src + (int64_t)h * D;            // q heads, then k heads, are consecutive in the row
+    const T* w = is_q ? q_w : k_w;
+    T* out = is_q ? src + (int64_t)h * D : dst_pool + (int64_t)(h - H) * D;
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) { const float v = to_f32(in[d]); row[d] = v; ss = fmaf(v, v, ss); }
+    float rstd = 1.f;
+    if (w) rstd = 1.0f / sqrtf(warp_reduce_sum(ss) / (float)D + eps);
+    __syncwarp();
+    if (w)
+      for (int d = lane; d < D; d += 32) row[d] = row[d] * rstd * to_f32(w[d]);
+    __syncwarp();
+    for (int d = lane; d < D; d += 32) {
+      float v = row[d];
+      if (d < rot_dims && cs) {
+        int i, partner;
+        bool first;
+        if (pairing == 0) { i = d >> 1; first = (d & 1) == 0; partner = first ? d + 1 : d - 1; }
+        else { first = d < half; i = first ? d : d - half; partner = first ? d + half : d - half; }
+        const float c = cs[i], s = cs[half + i], o = row[partner];
+        v = first ? v * c - o * s : v * c + o * s;
+      }
+      out[d] = from_f32<T>(v);
+    }
+    __syncwarp();                                  // the row is reused by the warp's next head
+  }
+  const T* vin = src + (int64_t)(H + G) * D;
+  T* vout = dst_pool + (int64_t)G * D;
+  for (int i = threadIdx.x; i < G * Dv; i += blockDim.x) vout[i] = vin[i];
+}
+
+}  // namespace
+
+extern "C" int b2l_rope_table_freqs(void* cos_sin_f32, const void* pos_i32, const void* freqs_f32, int64_t tokens,
+                                    int rot_dims, float magnitude, void* stream) {
+  B2L_REQUIRE(cos_sin_f32 && pos_i32 && freqs_f32, "rope_table_freqs: null pointer");
+  B2L_REQUIRE(rot_dims > 0 && rot_dims % 2 == 0, "rope_table_freqs: %d rotated entries", rot_dims);
+  if (tokens <= 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t total = tokens * (rot_dims / 2);
+  const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
+  b2l_launch(rope_table_freqs_kernel, dim3(grid), dim3(256), (size_t)0, st, (float*)cos_sin_f32, (const int*)pos_i32,
+             (const float*)freqs_f32, total, rot_dims / 2, magnitude);
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+extern "C" int b2l_head_norm_rope_prepare(void* qkv, int64_t qkv_row_stride, void* kv_pool, int64_t kv_row_stride,
+                                          const void* kv_rows_i32, const void* cos_sin_f32, const void* q_norm_weight,
+                                          const void* k_norm_weight, int64_t tokens, int heads, int kv_heads,
+                                          int head_dim, int v_head_dim, int rot_dims, int pairing, float eps, int dtype,
+                                          void* stream) {
+  B2L_REQUIRE(qkv && kv_pool && kv_rows_i32, "head_norm_rope_prepare: null pointer");
+  B2L_REQUIRE(heads > 0 && kv_heads > 0 && head_dim > 0 && v_head_dim > 0, "head_norm_rope_prepare: bad shape");
+  B2L_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= head_dim && (rot_dims == 0 || cos_sin_f32),
+              "head_norm_rope_prepare: %d rotated entries of %d", rot_dims, head_dim);
+  B2L_REQUIRE(pairing == 0 || pairing == 1, "head_norm_rope_prepare: pairing %d", pairing);
+  if (tokens <= 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = (size_t)kPrepWarps * head_dim * sizeof(float);
+  B2L_REQUIRE(smem <= 48 * 1024, "head_norm_rope_prepare: head_dim %d too large", head_dim);
+  B2L_DISPATCH_FLOAT(dtype, "head_norm_rope_prepare", {
+    b2l_launch(head_norm_rope_prepare_kernel<T>, dim3((unsigned)tokens), dim3(kPrepWarps * 32), smem, st, (T*)qkv,
+               qkv_row_stride, (T*)kv_pool, kv_row_stride, (const int*)kv_rows_i32, (const float*)cos_sin_f32,
+               (const T*)q_norm_weight, (const T*)k_norm_weight, heads, kv_heads, head_dim, v_head_dim, rot_dims,
+               pairing, eps);
+  });
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}

@@ -2,12 +2,14 @@
 // sequence s owns tokens [seq_start[s], seq_start[s+1]) of the flat batch, has seq_ctx[s] earlier tokens whose
 // effect lives in state slot seq_slot[s], and may bring any number of new tokens (1 = a decode step).
 //
-//   causal_conv_silu      out[t, c] = silu(bias[c] + sum_j w[c, K-1-j] * in[t-j, c]); inputs before the step come from
+//   causal_conv_silu      (`activation` 1; 0 = the plain convolution) out[t, c] = silu(bias[c] + sum_j w[c, K-1-j] * in[t-j, c]); inputs before the step come from
 //                         the slot's conv tail (the last K-1 inputs), inputs before the sequence are zero
 //   conv_tail_update      the slot's conv tail after the step (in place)
 //   ssm_scan              dt = softplus(dt_raw + dt_bias); S <- exp(-exp(A_log) dt) S + dt B x^T; y = S^T C + D x
 //                         S in fp32 registers for the whole step, read from / written to the slot once
-//                         (slot layout [head, n, p])
+//                         (slot layout [head, n, p]).  With `fixed_decay` (fp32 per head) the same kernel runs a
+//                         decayed linear attention: S <- decay_h S + B x^T, y = S^T C (dt = 1, no skip term), and
+//                         `silu_inputs` applies SiLU to x, B and C as they are staged (fp32)
 //   gated_group_norm      o = unit_rms_g(y * silu(z)) * w   in `groups` equal parts of the row
 // A sequence with seq_ctx == 0 starts from zero: its slot is never read, so slots need no clearing when reused.
 #include "common.cuh"
@@ -32,7 +34,7 @@ __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict
                                         const T* __restrict__ w, const T* __restrict__ bias,
                                         const T* __restrict__ tail, const int* __restrict__ seq_start,
                                         const int* __restrict__ seq_ctx, const int* __restrict__ seq_slot, int nseq,
-                                        int channels, int taps) {
+                                        int channels, int taps, int act) {
   pdl_prologue();
   const int tok = blockIdx.y;
   const int s = find_seq(seq_start, nseq, tok);
@@ -48,7 +50,7 @@ __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict
     else if (ctx + i >= 0) v = to_f32(tail[(slot * (taps - 1) + (taps - 1 + i)) * channels + c]);
     acc = fmaf(to_f32(w[(int64_t)c * taps + (taps - 1 - j)]), v, acc);
   }
-  out[(int64_t)tok * channels + c] = from_f32<T>(silu_f(acc));
+  out[(int64_t)tok * channels + c] = from_f32<T>(act ? silu_f(acc) : acc);
 }
 
 // The same with 16-byte accesses: one thread = VEC consecutive channels (channels, the input row stride and the
@@ -58,7 +60,7 @@ __global__ void causal_conv_silu_vec_kernel(T* __restrict__ out, const T* __rest
                                             const T* __restrict__ w, const T* __restrict__ bias,
                                             const T* __restrict__ tail, const int* __restrict__ seq_start,
                                             const int* __restrict__ seq_ctx, const int* __restrict__ seq_slot,
-                                            int nseq, int channels, int taps) {
+                                            int nseq, int channels, int taps, int act) {
   pdl_prologue();
   constexpr int VEC = 16 / (int)sizeof(T);
   const int tok = blockIdx.y;
@@ -108,7 +110,7 @@ __global__ void causal_conv_silu_vec_kernel(T* __restrict__ out, const T* __rest
   uint4 res;
   T* e = reinterpret_cast<T*>(&res);
 #pragma unroll
-  for (int k = 0; k < VEC; ++k) e[k] = from_f32<T>(silu_f(acc[k]));
+  for (int k = 0; k < VEC; ++k) e[k] = from_f32<T>(act ? silu_f(acc[k]) : acc[k]);
   *reinterpret_cast<uint4*>(out + (int64_t)tok * channels + c) = res;
 }
 
@@ -151,7 +153,8 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
     float* __restrict__ y, float* __restrict__ state, const T* __restrict__ xbc, int64_t xbc_stride,
     const T* __restrict__ dt_raw, int64_t dt_stride, const T* __restrict__ dt_bias, const T* __restrict__ a_log,
     const T* __restrict__ d_skip, const int* __restrict__ seq_start, const int* __restrict__ seq_ctx,
-    const int* __restrict__ seq_slot, int heads, int groups, int N, int P, int ctiles, int nslices) {
+    const int* __restrict__ seq_slot, int heads, int groups, int N, int P, int ctiles, int nslices,
+    const float* __restrict__ fixed_decay, int silu_inputs) {
   pdl_prologue();
   extern __shared__ __align__(16) float sm[];
   const int Np = nslices * NPT, cols = ctiles * 32 * CPL;
@@ -168,7 +171,10 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
   if (len <= 0) return;
   const int64_t slot = seq_slot[s];
   const int g = h / (heads / groups), inner = heads * P;
-  const float neg_a = -expf(to_f32(a_log[h])), bias = to_f32(dt_bias[h]), dsk = to_f32(d_skip[h]);
+  const bool fixed = fixed_decay != nullptr;
+  const float neg_a = fixed ? 0.f : -expf(to_f32(a_log[h])), bias = fixed ? 0.f : to_f32(dt_bias[h]);
+  const float dsk = fixed ? 0.f : to_f32(d_skip[h]), fdec = fixed ? fixed_decay[h] : 0.f;
+  auto act_in = [&](float v) { return silu_inputs ? silu_f(v) : v; };
   const int boff = inner + g * N, coff = inner + groups * N + g * N;
   const int nchunks = (len + kChunk - 1) / kChunk;
 
@@ -205,7 +211,7 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
             float* dst = (op ? sC : sB) + t * Np + n;
             const T* e = reinterpret_cast<const T*>(&raw[u]);
 #pragma unroll
-            for (int c = 0; c < VEC; ++c) dst[c] = to_f32(e[c]);
+            for (int c = 0; c < VEC; ++c) dst[c] = act_in(to_f32(e[c]));
           }
         }
       }
@@ -228,7 +234,7 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
             const int t = idx / xv, c = (idx - t * xv) * VEC;
             const T* e = reinterpret_cast<const T*>(&raw[u]);
 #pragma unroll
-            for (int k2 = 0; k2 < VEC; ++k2) sX[t * cols + c + k2] = to_f32(e[k2]);
+            for (int k2 = 0; k2 < VEC; ++k2) sX[t * cols + c + k2] = act_in(to_f32(e[k2]));
           }
         }
       }
@@ -237,21 +243,21 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
       for (int i = t0; i < tc * Np; i += nth) {
         const int t = i / Np, n = i - t * Np;
         const T* r = rows + (int64_t)t * xbc_stride;
-        const float bv = n < N ? to_f32(r[boff + n]) : 0.f;
-        const float cv = n < N ? to_f32(r[coff + n]) : 0.f;
+        const float bv = n < N ? act_in(to_f32(r[boff + n])) : 0.f;
+        const float cv = n < N ? act_in(to_f32(r[coff + n])) : 0.f;
         sB[i] = bv;
         sC[i] = cv;
       }
 #pragma unroll 8
       for (int i = t0; i < tc * cols; i += nth) {
         const int t = i / cols, c = i - t * cols;
-        sX[i] = (col0 + c < P) ? to_f32(rows[(int64_t)t * xbc_stride + h * P + col0 + c]) : 0.f;
+        sX[i] = (col0 + c < P) ? act_in(to_f32(rows[(int64_t)t * xbc_stride + h * P + col0 + c])) : 0.f;
       }
     }
     if (t0 < tc) {
-      const float dtv = softplus_f(to_f32(dt_raw[(int64_t)(start + c0 + t0) * dt_stride + h]) + bias);
+      const float dtv = fixed ? 1.0f : softplus_f(to_f32(dt_raw[(int64_t)(start + c0 + t0) * dt_stride + h]) + bias);
       sDt[t0] = dtv;
-      sDt[kChunk + t0] = expf(neg_a * dtv);
+      sDt[kChunk + t0] = fixed ? fdec : expf(neg_a * dtv);
     }
   };
   // y of chunk k from the slices' partial sums (nslices > 1)
@@ -452,7 +458,7 @@ __global__ void gated_group_norm_vec_kernel(T* __restrict__ o, const float* __re
 extern "C" int b2l_causal_conv_silu(void* out, const void* in, int64_t in_row_stride, const void* weight,
                                     const void* bias, void* tail, const void* seq_start, const void* seq_ctx,
                                     const void* seq_slot, int64_t num_seqs, int64_t tokens, int channels, int taps,
-                                    int dtype, void* stream) {
+                                    int activation, int dtype, void* stream) {
   B2L_REQUIRE(out && in && weight && bias && (tail || taps == 1) && seq_start && seq_ctx && seq_slot, "causal_conv_silu: null pointer");
   B2L_REQUIRE(channels > 0 && taps >= 1 && num_seqs >= 0 && tokens >= 0, "causal_conv_silu: bad shape");
   if (tokens == 0 || num_seqs == 0) return B2L_OK;
@@ -462,7 +468,8 @@ extern "C" int b2l_causal_conv_silu(void* out, const void* in, int64_t in_row_st
 #define B2L_CONV(TP)                                                                                                 \
   b2l_launch(causal_conv_silu_vec_kernel<T, TP>, dim3((unsigned)cdiv64(channels / VEC, 128), (unsigned)tokens), block, \
              (size_t)0, st, (T*)out, (const T*)in, in_row_stride, (const T*)weight, (const T*)bias, (const T*)tail,  \
-             (const int*)seq_start, (const int*)seq_ctx, (const int*)seq_slot, (int)num_seqs, channels, taps)
+             (const int*)seq_start, (const int*)seq_ctx, (const int*)seq_slot, (int)num_seqs, channels, taps,        \
+             activation)
   B2L_DISPATCH_FLOAT(dtype, "causal_conv_silu", {
     constexpr int VEC = 16 / (int)sizeof(T);
     const bool vec = channels % VEC == 0 && in_row_stride % VEC == 0 && (uintptr_t)in % 16 == 0 &&
@@ -475,7 +482,7 @@ extern "C" int b2l_causal_conv_silu(void* out, const void* in, int64_t in_row_st
     else
       b2l_launch(causal_conv_silu_kernel<T>, grid, block, (size_t)0, st, (T*)out, (const T*)in, in_row_stride,
                  (const T*)weight, (const T*)bias, (const T*)tail, (const int*)seq_start, (const int*)seq_ctx,
-                 (const int*)seq_slot, (int)num_seqs, channels, taps);
+                 (const int*)seq_slot, (int)num_seqs, channels, taps, activation);
     b2l_count_launch();
     if (taps > 1)
       b2l_launch(conv_tail_update_kernel<T>, grid2, block, (size_t)0, st, (T*)tail, (const T*)in, in_row_stride,
@@ -489,9 +496,10 @@ extern "C" int b2l_causal_conv_silu(void* out, const void* in, int64_t in_row_st
 extern "C" int b2l_ssm_scan(void* y_f32, void* state_f32, const void* xbc, int64_t xbc_row_stride, const void* dt_raw,
                             int64_t dt_row_stride, const void* dt_bias, const void* a_log, const void* d_skip,
                             const void* seq_start, const void* seq_ctx, const void* seq_slot, int64_t num_seqs,
-                            int heads, int groups, int state_size, int head_dim, int dtype, void* stream) {
-  B2L_REQUIRE(y_f32 && state_f32 && xbc && dt_raw && dt_bias && a_log && d_skip && seq_start && seq_ctx && seq_slot,
-              "ssm_scan: null pointer");
+                            int heads, int groups, int state_size, int head_dim, const void* fixed_decay_f32,
+                            int silu_inputs, int dtype, void* stream) {
+  B2L_REQUIRE(y_f32 && state_f32 && xbc && seq_start && seq_ctx && seq_slot, "ssm_scan: null pointer");
+  B2L_REQUIRE(fixed_decay_f32 || (dt_raw && dt_bias && a_log && d_skip), "ssm_scan: null pointer");
   B2L_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0 && state_size > 0 && head_dim > 0,
               "ssm_scan: bad geometry heads=%d groups=%d state=%d head_dim=%d", heads, groups, state_size, head_dim);
   B2L_REQUIRE(state_size <= 768, "ssm_scan: state size %d > 768", state_size);
@@ -518,7 +526,7 @@ extern "C" int b2l_ssm_scan(void* y_f32, void* state_f32, const void* xbc, int64
     b2l_launch(ssm_scan_kernel<T, NPTV, CPLV>, grid, block, smem, st, (float*)y_f32, (float*)state_f32,              \
                (const T*)xbc, xbc_row_stride, (const T*)dt_raw, dt_row_stride, (const T*)dt_bias, (const T*)a_log,   \
                (const T*)d_skip, (const int*)seq_start, (const int*)seq_ctx, (const int*)seq_slot, heads, groups,    \
-               state_size, head_dim, ctiles, nslices);                                                               \
+               state_size, head_dim, ctiles, nslices, (const float*)fixed_decay_f32, silu_inputs);                   \
   } while (0)
   B2L_DISPATCH_FLOAT(dtype, "ssm_scan", {
     if (cpl == 2) {

@@ -3,12 +3,14 @@ attention metadata, the KV pool + bump allocator, and the ModelRunner that drive
 
 from .attention_metadata import AttentionMetadata
 from .kv_cache_manager import KVCacheManager
-from .model_config import (DenseMlpSpec, LatentAttentionSpec, LayeredConfig, LayerSpec, Mamba2Spec, ModelConfig, MoeMlpSpec,
-                           PRESETS, SinkAttentionSpec)
+from .model_config import (BlockAttentionSpec, DecayAttentionSpec, DenseMlpSpec, LatentAttentionSpec, LayeredConfig,
+                           LayerSpec, Mamba2Spec, MinGruSpec, ModelConfig, MoeMlpSpec, PRESETS, RgLruSpec, SideBySideSpec,
+                           SinkAttentionSpec)
 from .model_runner import ModelRunner, RequestState
 from .ragged_batch import RaggedBatch
 from .state_manager import RecurrentStateManager
 
 __all__ = ["AttentionMetadata", "KVCacheManager", "ModelConfig", "PRESETS", "ModelRunner", "RequestState", "RaggedBatch",
            "RecurrentStateManager", "LayeredConfig", "LayerSpec", "Mamba2Spec", "SinkAttentionSpec", "DenseMlpSpec",
-           "LatentAttentionSpec", "MoeMlpSpec"]
+           "LatentAttentionSpec", "MoeMlpSpec", "MinGruSpec", "RgLruSpec", "BlockAttentionSpec", "DecayAttentionSpec",
+           "SideBySideSpec"]

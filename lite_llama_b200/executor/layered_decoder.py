@@ -23,6 +23,12 @@ Designs registered here:
     layer scale, latent attention (low-rank query and key/value latents, a shared rotated key part, sliding window,
     per-head sigmoid output gate), routed experts (sigmoid router with selection bias and group-limited choice, exact
     GELU, a shared expert), layers that share another layer's weights, soft-capped logits.
+  * ``Tisosun``: normed embedding; PARALLEL blocks ``x <- x + mixer(norm1(x)) + ff(norm2(x))`` with a gated feed-forward,
+    a gated low-rank per-layer token input after the block, and a learned depth-weighted average of all layer results
+    in front of every layer and of the output; mixers: a minimal GRU, a real-gated linear recurrent unit behind a
+    short convolution, and softmax attention (biased projections, per-head q / k norm, neighbour-paired rotary
+    positions with frequency interpolation by parts, soft cap, block-diagonal causal mask) side by side with decayed
+    linear attention.
 """
 
 from __future__ import annotations
@@ -33,26 +39,36 @@ import torch
 
 from ..kernels import (
     attn_prepare,
+    branch_sum_residual,
     causal_conv_silu,
+    depth_mix_norms,
     embed_positions,
+    embed_rmsnorm,
     gated_group_norm,
+    gated_scan,
     gelu,
+    gelu_mul_gather,
     grouped_experts,
     head_linear,
+    head_norm_rope_prepare,
     latent_prepare,
     linear,
+    norm_sigmoid_gate,
     post_norm_residual,
     relu_squared,
     rmsnorm_from_f32,
     rope_heads,
     rope_table,
+    rope_table_freqs,
+    rotary_frequencies,
     route_sigmoid_groups,
     sink_attention,
     softcap_to_f32,
     ssm_scan,
+    swiglu_forward,
 )
-from .model_config import (DenseMlpSpec, LatentAttentionSpec, LayeredConfig, LayerSpec, Mamba2Spec, MoeMlpSpec,
-                           SinkAttentionSpec)
+from .model_config import (BlockAttentionSpec, DecayAttentionSpec, DenseMlpSpec, LatentAttentionSpec, LayeredConfig,
+                           LayerSpec, Mamba2Spec, MinGruSpec, MoeMlpSpec, RgLruSpec, SideBySideSpec, SinkAttentionSpec)
 from .ragged_batch import RaggedBatch
 from .registry import Architecture, register
 
@@ -68,6 +84,8 @@ class LayeredLayerWeights:
     pre2: torch.Tensor | None = None
     ls1: torch.Tensor | None = None
     ls2: torch.Tensor | None = None
+    side: dict[str, torch.Tensor] | None = None          # per-layer token input: gate, proj, norm
+    depth: torch.Tensor | None = None                    # depth-average coefficients over [embedding, layer results]
 
 
 @dataclass
@@ -77,6 +95,8 @@ class LayeredWeights:
     final_norm: torch.Tensor
     head: torch.Tensor
     layers: list[LayeredLayerWeights] = field(default_factory=list)
+    embed_norm: torch.Tensor | None = None
+    side_embed: torch.Tensor | None = None               # [vocab, layers * token_side_dim]
 
     def nbytes_per_step(self) -> int:
         """Weight bytes one step streams (embedding / position gathers excluded)."""
@@ -86,7 +106,7 @@ class LayeredWeights:
             if id(lw) in seen:                           # a layer that shares another one's weights
                 continue
             seen.add(id(lw))
-            for d in (lw.mix, lw.mlp or {}):
+            for d in (lw.mix, lw.mlp or {}, lw.side or {}):
                 total += sum(t.numel() * t.element_size() for t in d.values())
         return total
 
@@ -102,7 +122,7 @@ class StepContext:
         self.table = table
         self.states = states
         self.v_first: torch.Tensor | None = None
-        self._rope: dict[tuple[int, float], torch.Tensor | None] = {}
+        self._rope: dict[tuple, torch.Tensor | None] = {}
 
     def rope(self, rot_dims: int, rot_base: float) -> torch.Tensor | None:
         """The step's [cos | sin] table for these rotary constants, built once and shared by the layers."""
@@ -110,6 +130,26 @@ class StepContext:
         if key not in self._rope:
             self._rope[key] = rope_table(self.batch.positions, rot_dims, rot_base)
         return self._rope[key]
+
+    def rope_freqs(self, freqs: torch.Tensor, magnitude: float) -> torch.Tensor:
+        """The step's magnitude * [cos | sin] table for a frequency vector (one per rotary configuration; layers with
+        equal constants share the tensor and so the table)."""
+        key = (freqs.data_ptr(), magnitude)
+        if key not in self._rope:
+            self._rope[key] = rope_table_freqs(self.batch.positions, freqs, magnitude)
+        return self._rope[key]
+
+
+@dataclass
+class Branches:
+    """A mixer's output as up to two branches that the residual kernel norms (plain weights) and averages:
+    ``scale * (unit_rms(a) * a_weight + unit_rms(b) * b_weight)``."""
+
+    a: torch.Tensor
+    a_weight: torch.Tensor | None
+    b: torch.Tensor | None = None
+    b_weight: torch.Tensor | None = None
+    scale: float = 1.0
 
 
 def mamba2_mixer(li: int, spec: Mamba2Spec, w: dict[str, torch.Tensor], x: torch.Tensor, ctx: StepContext,
@@ -203,6 +243,75 @@ def latent_attention_mixer(li: int, spec: LatentAttentionSpec, w: dict[str, torc
     return linear(out, w["o"])
 
 
+def min_gru_mixer(li: int, spec: MinGruSpec, w: dict[str, torch.Tensor], x: torch.Tensor, ctx: StepContext,
+                  eps: float) -> torch.Tensor:
+    """One biased projection [update gate | candidate | output gate] -> the element-wise recurrence against the slot's
+    fp32 state (gates in fp32, output gate fused) -> out-projection."""
+    b, n = ctx.batch, spec.width
+    proj = linear(x, w["in"], w["in_b"])
+    y = gated_scan("mingru", ctx.states.ssm_state[li], proj[:, :n], proj[:, n:2 * n], proj[:, 2 * n:3 * n], b.seq_start,
+                   b.seq_ctx, b.seq_slot)
+    return linear(y, w["o"])
+
+
+def rg_lru_mixer(li: int, spec: RgLruSpec, w: dict[str, torch.Tensor], x: torch.Tensor, ctx: StepContext,
+                 eps: float) -> torch.Tensor:
+    """One biased projection [GELU branch | recurrence branch] -> causal convolution of the recurrence branch (tail
+    kept per slot) -> the two block-diagonal gate projections -> the recurrence (biases, sigmoids, decay, input
+    scaling, GELU of the other branch and the product in one kernel, fp32) -> out-projection."""
+    b, n = ctx.batch, spec.width
+    per = n // spec.blocks
+    proj = linear(x, w["in"], w["in_b"])
+    u = causal_conv_silu(proj, n, n, w["conv"], w["conv_b"], ctx.states.conv_tail[li], b.seq_start, b.seq_ctx,
+                         b.seq_slot, activation=False)
+    gates = torch.empty((b.tokens, 2 * n), dtype=u.dtype, device=u.device)
+    head_linear(gates[:, :n], per, u, per, w["ra"])
+    head_linear(gates[:, n:], per, u, per, w["ri"])
+    y = gated_scan("rglru", ctx.states.ssm_state[li], u, gates[:, :n], gates[:, n:], b.seq_start, b.seq_ctx, b.seq_slot,
+                   p3=proj[:, :n], bias_r=w["ra_b"], bias_i=w["ri_b"], lam=w["lam"], decay_scale=spec.decay_scale)
+    return linear(y, w["o"])
+
+
+def side_by_side_mixer(li: int, spec: SideBySideSpec, w: dict[str, torch.Tensor], x: torch.Tensor, ctx: StepContext,
+                       eps: float) -> Branches:
+    """ONE projection for both halves, [q | k | v (biased) | pad || v' | k' | q' | gate'].  Left: per-head norms,
+    rotation and the cache write in one kernel, attention over the pool under the block-diagonal mask, out-projection.
+    Right: the fixed-decay scan against the slot's fp32 memory (SiLU applied as the scan reads its inputs), row norm
+    and sigmoid gate, out-projection.  The two outputs go to the residual kernel as branches."""
+    b, L, R = ctx.batch, spec.left, spec.right
+    proj = linear(x, w["in"], w["in_b"])
+    # ---- left: softmax attention over the pool
+    pool = ctx.kv_buffer[li]
+    cos_sin = ctx.rope_freqs(w["freqs"], spec_magnitude(L)) if L.rot_dims else None
+    head_norm_rope_prepare(proj, pool, b.kv_rows, cos_sin, w.get("q_norm"), w.get("k_norm"), L.heads, L.kv_heads,
+                           L.head_dim, L.v_head_dim, L.rot_dims, eps, L.pairing)
+    att = torch.empty((b.tokens, L.heads * L.v_head_dim), dtype=proj.dtype, device=proj.device)
+    common = (L.heads, L.kv_heads, L.head_dim, L.v_head_dim, L.scale, L.softcap)
+    if b.num_portions:
+        sink_attention(att, proj, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.portion_list, b.num_portions,
+                       b.max_portion, None, *common, block=L.block)
+    if b.num_singles:
+        keys = b.max_single_ctx + 1
+        splits, per = split_plan(min(keys, L.block) if L.block else keys)
+        sink_attention(att, proj, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.single_list, b.num_singles, 1,
+                       None, *common, num_splits=splits, split_keys=per, block=L.block)
+    left = linear(att, w["left_o"])
+    # ---- right: decayed linear attention over the slot's memory
+    r0 = -(-(L.heads * L.head_dim + L.kv_heads * (L.head_dim + L.v_head_dim)) // 8) * 8     # padded attention half
+    inner = R.heads * R.v_head_dim
+    xbc = proj[:, r0:r0 + inner + 2 * R.heads * R.head_dim]
+    y = ssm_scan(xbc, None, None, None, None, ctx.states.ssm_state[li], b.seq_start, b.seq_ctx, b.seq_slot, R.heads,
+                 R.heads, R.head_dim, R.v_head_dim, fixed_decay=w["decay"], silu_inputs=True)
+    gate = proj[:, r0 + inner + 2 * R.heads * R.head_dim:r0 + 2 * inner + 2 * R.heads * R.head_dim]
+    right = linear(norm_sigmoid_gate(y, gate, w["right_norm"], eps), w["right_o"])
+    return Branches(left, w["left_out"], right, w["right_out"], 0.5)
+
+
+def spec_magnitude(spec: BlockAttentionSpec) -> float:
+    return rotary_frequencies(spec.rot_dims, spec.rot_base, spec.rot_factor, spec.rot_original, spec.rot_fast,
+                              spec.rot_slow)[1]
+
+
 def _activate(kind: str, x: torch.Tensor) -> torch.Tensor:
     if kind == "relu2":
         return relu_squared(x)
@@ -214,6 +323,11 @@ def _activate(kind: str, x: torch.Tensor) -> torch.Tensor:
 
 
 def dense_feed_forward(spec: DenseMlpSpec, w: dict[str, torch.Tensor], x: torch.Tensor) -> torch.Tensor:
+    if spec.gated:                                   # [gate | up] is one product; silu(gate) * up one kernel
+        if spec.activation != "silu":
+            raise ValueError(f"unknown gated feed-forward activation {spec.activation!r}")
+        gu = linear(x, w["gate_up"])
+        return linear(swiglu_forward(gu[:, :spec.ff], gu[:, spec.ff:]), w["down"])
     return linear(_activate(spec.activation, linear(x, w["up"])), w["down"])
 
 
@@ -227,7 +341,8 @@ def moe_feed_forward(spec: MoeMlpSpec, w: dict[str, torch.Tensor], x: torch.Tens
     return grouped_experts(x, w["up"], w["down"], weights, ids, addend=shared, activation=spec.activation)
 
 
-MIXERS = {"mamba2": mamba2_mixer, "attention": sink_attention_mixer, "latent_attention": latent_attention_mixer}
+MIXERS = {"mamba2": mamba2_mixer, "attention": sink_attention_mixer, "latent_attention": latent_attention_mixer,
+          "mingru": min_gru_mixer, "rglru": rg_lru_mixer, "parallel": side_by_side_mixer}
 FEED_FORWARDS = {"dense": dense_feed_forward, "moe": moe_feed_forward}
 
 
@@ -246,6 +361,8 @@ class LayeredDecoder:
         design soft-caps its logits)."""
         cfg, eps, off, kind = self.cfg, self.cfg.rms_norm_eps, self.norm_offset, self.cfg.norm_kind
         ctx = StepContext(batch, kv_buffer, table, states)
+        if cfg.parallel_block:
+            return self._forward_parallel(tokens, ctx, want_rows)
         pre = cfg.pre_norm
         resid, act = embed_positions(tokens, batch.positions, self.w.embed, self.w.pos, want_act=not pre,
                                      scale=cfg.embed_scale)
@@ -271,9 +388,60 @@ class LayeredDecoder:
         if want_rows is not None and want_rows.numel() == 0:
             return torch.empty((0, cfg.vocab_size), dtype=torch.float32 if cfg.logit_softcap else self.dtype,
                                device=resid.device)
-        hidden = rmsnorm_from_f32(resid, self.w.final_norm, eps, off, want_rows, kind)
+        return self._head(resid, want_rows)
+
+    def _head(self, resid: torch.Tensor, want_rows: torch.Tensor | None) -> torch.Tensor:
+        cfg = self.cfg
+        hidden = rmsnorm_from_f32(resid, self.w.final_norm, cfg.rms_norm_eps, self.norm_offset, want_rows, cfg.norm_kind)
         logits = linear(hidden, self.w.head)
         return softcap_to_f32(logits, cfg.logit_softcap) if cfg.logit_softcap else logits
+
+    def _forward_parallel(self, tokens: torch.Tensor, ctx: StepContext, want_rows: torch.Tensor | None) -> torch.Tensor:
+        """Parallel blocks over a stack of fp32 results: level 0 is the (normed) embedding, level i + 1 the result of
+        layer i.  Per layer: one kernel forms the layer's input (the depth-weighted sum of the levels so far, or the
+        last level) IN the next level and both input norms from one statistic; mixer and feed-forward run; one kernel
+        adds their (normed, averaged) outputs to the level; the token input (gate product, GELU * table row, projection)
+        joins through the output-norm kernel.  The level then holds the layer's result."""
+        cfg, w, eps, off = self.cfg, self.w, self.cfg.rms_norm_eps, self.norm_offset
+        if cfg.norm_kind != "rms" or cfg.pre_norm or cfg.layer_scale:
+            raise ValueError("parallel blocks use RMS input norms only")
+        T, n, count = tokens.numel(), cfg.hidden_size, len(cfg.layers)
+        levels = count + 2 if cfg.depth_average else 2           # the last level takes the mix the output norm reads
+        stack = torch.empty((levels, T, n), dtype=torch.float32, device=tokens.device)
+        if cfg.embed_norm:
+            embed_rmsnorm(tokens, w.embed, w.embed_norm, eps, off, cfg.embed_scale, out=stack[0])
+        else:
+            stack[0].copy_(embed_positions(tokens, ctx.batch.positions, w.embed, w.pos, want_act=False,
+                                           scale=cfg.embed_scale)[0])
+        coef = None
+        for li, (spec, lw) in enumerate(zip(cfg.layers, w.layers)):
+            # without a depth average two levels alternate: the previous result is the input
+            src = stack[:li + 1] if cfg.depth_average else stack[li % 2:li % 2 + 1]
+            x = stack[li + 1] if cfg.depth_average else stack[(li + 1) % 2]
+            _, h1, h2 = depth_mix_norms(src, src.shape[0], coef, lw.pre1, lw.pre2 if spec.mlp is not None else None, eps,
+                                        off, out=x)
+            y = MIXERS[spec.kind](li, spec.mixer, lw.mix, h1, ctx, eps)
+            f = FEED_FORWARDS[spec.mlp.kind](spec.mlp, lw.mlp, h2) if spec.mlp is not None else None
+            br = y if isinstance(y, Branches) else Branches(y, None)
+            act = branch_sum_residual(x, br.a, br.a_weight, br.b, br.b_weight, f, eps, br.scale,
+                                      want_act=lw.side is not None)
+            if lw.side is not None:
+                d = cfg.token_side_dim
+                z = linear(x if act is None else act, lw.side["gate"])
+                g = gelu_mul_gather(z, tokens, w.side_embed, li * d)
+                post_norm_residual(x, linear(g, lw.side["proj"]), lw.side["norm"], eps, 0.0, want_act=False)
+            coef = lw.depth
+            if self.layer_trace is not None:
+                self.layer_trace.append(x.clone())
+        if cfg.depth_average and coef is not None:
+            src, final = stack[:count + 1], stack[count + 1]
+            depth_mix_norms(src, count + 1, coef, None, None, eps, off, out=final, dtype=self.dtype)
+        else:
+            final = stack[count] if cfg.depth_average else stack[count % 2]
+        if want_rows is not None and want_rows.numel() == 0:
+            return torch.empty((0, cfg.vocab_size), dtype=torch.float32 if cfg.logit_softcap else self.dtype,
+                               device=tokens.device)
+        return self._head(final, want_rows)
 
 
 # ---------------------------------------------------------------------------------------------- Gufotar plumbing #
@@ -516,3 +684,179 @@ _PESIVIK_SOURCES = ("gemm_dense", "gemm_simt", "gemm_rows_mma", "residual_stream
                     "moe_routing", "elementwise")
 register(Architecture("Pesivik", parse_pesivik_config, map_pesivik_weights, LayeredDecoder, ragged_steps=True,
                       sources=_PESIVIK_SOURCES))
+
+
+# ---------------------------------------------------------------------------------------------- Tisosun plumbing #
+def _block_attention_spec(m: dict) -> BlockAttentionSpec:
+    rot = m.get("rot") or {}
+    sc = rot.get("scaling") or {}
+    return BlockAttentionSpec(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), head_dim=int(m["dim"]),
+                              v_head_dim=int(m.get("vdim", m["dim"])), scale=float(m["scale"]),
+                              softcap=float(m.get("softcap") or 0.0), block=int((m.get("mask") or {}).get("size", 0)),
+                              rot_dims=int(rot.get("dims", 0)), rot_base=float(rot.get("base", 10000.0)),
+                              rot_factor=float(sc.get("factor", 1.0)), rot_original=float(sc.get("original", 0.0)),
+                              rot_fast=float(sc.get("fast", 0.0)), rot_slow=float(sc.get("slow", 0.0)))
+
+
+def parse_tisosun_config(raw: dict) -> LayeredConfig:
+    layers = []
+    for entry in raw["layers"]:
+        kind, m = entry["type"], entry["mixer"]
+        if kind == "mingru":
+            mixer = MinGruSpec(width=int(m["width"]))
+        elif kind == "rglru":
+            mixer = RgLruSpec(width=int(m["width"]), blocks=int(m.get("blocks", 1)), conv=int(m.get("conv", 1)))
+        elif kind == "parallel":
+            r = m["right"]
+            mixer = SideBySideSpec(_block_attention_spec(m["left"]),
+                                   DecayAttentionSpec(heads=int(r["heads"]), head_dim=int(r["dim"]),
+                                                      v_head_dim=int(r.get("vdim", r["dim"])),
+                                                      decay=tuple(float(d) for d in r["decay"])))
+        else:
+            raise ValueError(f"unknown layer type {kind!r}")
+        mlp = entry.get("mlp")
+        if mlp is not None and mlp.get("kind", "dense") != "dense":
+            raise ValueError(f"unknown feed-forward kind {mlp.get('kind')!r}")
+        layers.append(LayerSpec(kind, mixer, DenseMlpSpec(ff=int(mlp["ff"]), activation="silu", gated=True)
+                                if mlp is not None else None))
+    return LayeredConfig(name=raw.get("architecture", "Tisosun"), hidden_size=int(raw["width"]),
+                         vocab_size=int(raw["vocab"]), max_seq_len=0, rms_norm_eps=float(raw["norm"]["eps"]),
+                         layers=tuple(layers), norm_weight_offset=1.0, learned_positions=False, parallel_block=True,
+                         embed_norm=True, token_side_dim=int((raw.get("token_side") or {}).get("dim", 0)),
+                         depth_average=True)
+
+
+def _pad_rows(t: torch.Tensor, multiple: int) -> torch.Tensor:
+    pad = -t.shape[0] % multiple
+    return torch.cat([t, t.new_zeros((pad, *t.shape[1:]))], dim=0) if pad else t
+
+
+def map_tisosun_weights(cfg: LayeredConfig, tensors: dict[str, torch.Tensor], device: str,
+                        dtype: torch.dtype) -> LayeredWeights:
+    """Checkpoint names -> the decoder's weights.  Every mixer's input projections are row-concatenated into one GEMM
+    weight with one bias vector (zeros where a projection has none); the attention half is padded with zero rows to a
+    multiple of 8 so that the linear-attention half starts on a 16-byte boundary, and its columns are ordered
+    [values | keys | queries | gate], the layout the scan kernel reads.  Decays and rotary frequencies are fp32."""
+
+    def get(name: str) -> torch.Tensor:
+        if name not in tensors:
+            raise KeyError(f"checkpoint has no tensor {name!r}")
+        return tensors[name].to(device=device, dtype=dtype).contiguous()
+
+    def zeros(n: int) -> torch.Tensor:
+        return torch.zeros(n, dtype=dtype, device=device)
+
+    out = LayeredWeights(embed=get("embed"), pos=None, final_norm=get("final.norm"), head=get("head"),
+                         embed_norm=get("embed.norm"), side_embed=get("side.embed") if cfg.token_side_dim else None)
+    freq_cache: dict[tuple, torch.Tensor] = {}
+    for i, spec in enumerate(cfg.layers):
+        p, m = f"l{i}.mix.", spec.mixer
+        if isinstance(m, MinGruSpec):
+            mix = {"in": torch.cat([get(p + "z"), get(p + "x"), get(p + "g")], dim=0).contiguous(),
+                   "in_b": torch.cat([get(p + "z.b"), get(p + "x.b"), zeros(m.width)]), "o": get(p + "o")}
+        elif isinstance(m, RgLruSpec):
+            mix = {"in": torch.cat([get(p + "y"), get(p + "x")], dim=0).contiguous(),
+                   "in_b": torch.cat([get(p + "y.b"), get(p + "x.b")]), "conv": get(p + "conv"),
+                   "conv_b": get(p + "conv.b"), "ra": get(p + "ra"), "ri": get(p + "ri"),
+                   "ra_b": get(p + "ra.b").reshape(-1), "ri_b": get(p + "ri.b").reshape(-1), "lam": get(p + "lam"),
+                   "o": get(p + "o")}
+        else:
+            L, R = m.left, m.right
+            lq = _pad_rows(torch.cat([get(p + "left.q"), get(p + "left.k"), get(p + "left.v")], dim=0), 8)
+            lb = _pad_rows(torch.cat([get(p + "left.q.b"), get(p + "left.k.b"), get(p + "left.v.b")]), 8)
+            rq = torch.cat([get(p + "right.v"), get(p + "right.k"), get(p + "right.q"), get(p + "right.g")], dim=0)
+            key = (L.rot_dims, L.rot_base, L.rot_factor, L.rot_original, L.rot_fast, L.rot_slow)
+            if L.rot_dims and key not in freq_cache:
+                freq_cache[key] = torch.tensor(rotary_frequencies(*key)[0], dtype=torch.float64).to(
+                    device=device, dtype=torch.float32)
+            mix = {"in": torch.cat([lq, rq], dim=0).contiguous(), "in_b": torch.cat([lb, zeros(rq.shape[0])]),
+                   "q_norm": get(p + "left.q.norm"), "k_norm": get(p + "left.k.norm"), "left_o": get(p + "left.o"),
+                   "right_norm": get(p + "right.norm"), "right_o": get(p + "right.o"), "left_out": get(p + "left.out"),
+                   "right_out": get(p + "right.out"),
+                   "decay": torch.tensor(R.decay, dtype=torch.float64).to(device=device, dtype=torch.float32)}
+            if L.rot_dims:
+                mix["freqs"] = freq_cache[key]
+        lw = LayeredLayerWeights(norm1=None, mix=mix, pre1=get(f"l{i}.norm1"))
+        if spec.mlp is not None:
+            lw.pre2 = get(f"l{i}.norm2")
+            lw.mlp = {"gate_up": torch.cat([get(f"l{i}.mlp.gate"), get(f"l{i}.mlp.up")], dim=0).contiguous(),
+                      "down": get(f"l{i}.mlp.down")}
+        if cfg.token_side_dim:
+            lw.side = {"gate": get(f"l{i}.side.gate"), "proj": get(f"l{i}.side.proj"), "norm": get(f"l{i}.side.norm")}
+        if cfg.depth_average:
+            lw.depth = get(f"l{i}.dwa")
+        out.layers.append(lw)
+    return out
+
+
+def tisosun_tensor_shapes(cfg: LayeredConfig) -> dict[str, tuple[int, ...]]:
+    """Checkpoint tensor names and shapes of a configuration (random initialisation, shape checks)."""
+    w, d = cfg.hidden_size, cfg.token_side_dim
+    shapes: dict[str, tuple[int, ...]] = {"embed": (cfg.vocab_size, w), "embed.norm": (w,)}
+    if d:
+        shapes["side.embed"] = (cfg.vocab_size, d * len(cfg.layers))
+    for i, spec in enumerate(cfg.layers):
+        p, m = f"l{i}.mix.", spec.mixer
+        shapes[f"l{i}.norm1"] = (w,)
+        if isinstance(m, MinGruSpec):
+            shapes.update({p + "z": (m.width, w), p + "z.b": (m.width,), p + "x": (m.width, w), p + "x.b": (m.width,),
+                           p + "g": (m.width, w), p + "o": (w, m.width)})
+        elif isinstance(m, RgLruSpec):
+            per = m.width // m.blocks
+            shapes.update({p + "y": (m.width, w), p + "y.b": (m.width,), p + "x": (m.width, w), p + "x.b": (m.width,),
+                           p + "conv": (m.width, m.conv), p + "conv.b": (m.width,), p + "ra": (m.blocks, per, per),
+                           p + "ra.b": (m.blocks, per), p + "ri": (m.blocks, per, per), p + "ri.b": (m.blocks, per),
+                           p + "lam": (m.width,), p + "o": (w, m.width)})
+        else:
+            L, R = m.left, m.right
+            shapes.update({p + "left.q": (L.heads * L.head_dim, w), p + "left.q.b": (L.heads * L.head_dim,),
+                           p + "left.k": (L.kv_heads * L.head_dim, w), p + "left.k.b": (L.kv_heads * L.head_dim,),
+                           p + "left.v": (L.kv_heads * L.v_head_dim, w), p + "left.v.b": (L.kv_heads * L.v_head_dim,),
+                           p + "left.q.norm": (L.head_dim,), p + "left.k.norm": (L.head_dim,),
+                           p + "left.o": (w, L.heads * L.v_head_dim),
+                           p + "right.q": (R.heads * R.head_dim, w), p + "right.k": (R.heads * R.head_dim, w),
+                           p + "right.v": (R.heads * R.v_head_dim, w), p + "right.g": (R.heads * R.v_head_dim, w),
+                           p + "right.o": (w, R.heads * R.v_head_dim), p + "right.norm": (R.heads * R.v_head_dim,),
+                           p + "left.out": (w,), p + "right.out": (w,)})
+        if spec.mlp is not None:
+            shapes.update({f"l{i}.norm2": (w,), f"l{i}.mlp.gate": (spec.mlp.ff, w), f"l{i}.mlp.up": (spec.mlp.ff, w),
+                           f"l{i}.mlp.down": (w, spec.mlp.ff)})
+        if cfg.depth_average:
+            shapes[f"l{i}.dwa"] = (i + 2,)
+        if d:
+            shapes.update({f"l{i}.side.gate": (d, w), f"l{i}.side.proj": (w, d), f"l{i}.side.norm": (w,)})
+    shapes.update({"final.norm": (w,), "head": (cfg.vocab_size, w)})
+    return shapes
+
+
+def random_tisosun_tensors(cfg: LayeredConfig, seed: int = 0) -> dict[str, torch.Tensor]:
+    """Seeded random bf16 tensors with checkpoint names (benchmarks and tests; no trained checkpoints exist offline)."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tisosun_tensor_shapes(cfg).items():
+        leaf = name.rsplit(".", 1)[-1]
+        if leaf == "dwa":                                     # mostly the newest result, some of every older one
+            t = 0.15 * torch.randn(shape, generator=g)
+            t[-1] += 0.8
+        elif leaf == "conv":
+            t = 0.4 * torch.randn(shape, generator=g)
+        elif name.endswith("side.embed"):
+            t = torch.randn(shape, generator=g)
+        elif len(shape) >= 2:
+            t = torch.randn(shape, generator=g) / (shape[-1] ** 0.5)
+        elif leaf == "lam":
+            t = -1.0 + 0.7 * torch.randn(shape, generator=g)
+        elif leaf == "b":
+            t = 0.2 * torch.randn(shape, generator=g)
+        elif leaf in ("norm1", "norm2") or name in ("embed.norm", "final.norm"):
+            t = 0.1 * torch.randn(shape, generator=g)         # stored as the distance from one
+        else:                                                 # plain norm weights
+            t = 1.0 + 0.1 * torch.randn(shape, generator=g)
+        out[name] = t.to(torch.bfloat16)
+    return out
+
+
+_TISOSUN_SOURCES = ("gemm_dense", "gemm_simt", "gemm_rows_mma", "residual_stream", "parallel_stream", "gated_recurrence",
+                    "rotary_heads", "ssm_scan", "attention_sink", "elementwise")
+register(Architecture("Tisosun", parse_tisosun_config, map_tisosun_weights, LayeredDecoder, ragged_steps=True,
+                      sources=_TISOSUN_SOURCES))

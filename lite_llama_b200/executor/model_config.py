@@ -99,6 +99,14 @@ class Mamba2Spec:
     def in_rows(self) -> int:                       # [z | x | B | C | dt]
         return 2 * self.inner + 2 * self.groups * self.state + self.heads
 
+    @property
+    def state_shape(self) -> tuple[int, ...]:       # per request slot, fp32
+        return (self.heads, self.state, self.head_dim)
+
+    @property
+    def conv_tail_shape(self) -> tuple[int, int] | None:      # per request slot, activation dtype
+        return (max(self.conv - 1, 1), self.conv_channels)
+
     def validate(self) -> None:
         if self.heads % self.groups or self.inner % self.norm_groups or self.conv < 1 or self.state > 768:
             raise ValueError(f"unsupported state-space mixer geometry: {self}")
@@ -160,10 +168,134 @@ class LatentAttentionSpec:
 
 
 @dataclass(frozen=True)
+class MinGruSpec:
+    """Minimal gated recurrent unit: ``width`` channels, one fp32 state value per channel; update gate, candidate
+    and output gate read the current token only."""
+
+    width: int
+
+    @property
+    def state_shape(self) -> tuple[int, ...]:
+        return (self.width,)
+
+    conv_tail_shape = None
+
+    def validate(self) -> None:
+        if self.width < 1:
+            raise ValueError(f"unsupported recurrent mixer geometry: {self}")
+
+
+@dataclass(frozen=True)
+class RgLruSpec:
+    """Recurrent block around a real-gated linear recurrent unit: a GELU branch and a recurrence branch of ``width``
+    channels each; the recurrence branch passes a ``conv``-tap causal convolution (no activation), its two gates are
+    block-diagonal projections in ``blocks`` parts, the decay is ``exp(-decay_scale * r * softplus(lam))``."""
+
+    width: int
+    blocks: int
+    conv: int
+    decay_scale: float = 8.0
+
+    @property
+    def state_shape(self) -> tuple[int, ...]:
+        return (self.width,)
+
+    @property
+    def conv_tail_shape(self) -> tuple[int, int] | None:
+        return (max(self.conv - 1, 1), self.width)
+
+    def validate(self) -> None:
+        if self.width < 1 or self.blocks < 1 or self.width % self.blocks or self.conv < 1:
+            raise ValueError(f"unsupported recurrent mixer geometry: {self}")
+
+
+@dataclass(frozen=True)
+class BlockAttentionSpec:
+    """Softmax attention with biased projections, a per-head RMS norm of q and k (one ``[head_dim]`` weight each,
+    shared by the heads), rotary positions on the first ``rot_dims`` entries of every head (``pairing``: "neighbours"
+    = entries 2i, 2i+1; "halves" = i, i + rot_dims/2) with frequency interpolation by parts (``rot_factor`` > 1: see
+    ``kernels.rotary_frequencies``), a ``tanh`` soft cap (0: none) and a block-diagonal causal mask: position p sees
+    the positions of its own run of ``block`` that are not after it (0: plain causal)."""
+
+    heads: int
+    kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    scale: float
+    softcap: float = 0.0
+    block: int = 0
+    rot_dims: int = 0
+    rot_base: float = 10000.0
+    rot_factor: float = 1.0
+    rot_original: float = 0.0
+    rot_fast: float = 0.0
+    rot_slow: float = 0.0
+    pairing: str = "neighbours"
+
+    def validate(self) -> None:
+        if min(self.heads, self.kv_heads, self.head_dim, self.v_head_dim) < 1 or self.heads % self.kv_heads or \
+                self.v_head_dim > 256 or self.rot_dims % 2 or not 0 <= self.rot_dims <= self.head_dim or self.block < 0 \
+                or self.pairing not in ("neighbours", "halves"):
+            raise ValueError(f"unsupported attention geometry: {self}")
+
+    @property
+    def cache_row_width(self) -> int:                  # all K heads, then all V heads, padded to 16-byte vectors
+        return -(-self.kv_heads * (self.head_dim + self.v_head_dim) // 8) * 8
+
+
+@dataclass(frozen=True)
+class DecayAttentionSpec:
+    """Linear attention with one fixed decay per head: q, k (``heads x head_dim``) and v (``heads x v_head_dim``)
+    pass SiLU, the memory ``S_h <- decay_h S_h + k v^T`` (fp32, ``head_dim x v_head_dim``) answers ``S_h^T q``; the
+    joined heads are RMS-normed as one row, gated by a sigmoid projection and projected out."""
+
+    heads: int
+    head_dim: int
+    v_head_dim: int
+    decay: tuple[float, ...]
+
+    @property
+    def state_shape(self) -> tuple[int, ...]:
+        return (self.heads, self.head_dim, self.v_head_dim)
+
+    conv_tail_shape = None
+
+    def validate(self) -> None:
+        if min(self.heads, self.head_dim, self.v_head_dim) < 1 or len(self.decay) != self.heads or self.head_dim > 768 \
+                or not all(0.0 <= d <= 1.0 for d in self.decay):
+            raise ValueError(f"unsupported linear attention geometry: {self}")
+
+
+@dataclass(frozen=True)
+class SideBySideSpec:
+    """Two mixers that read the same input: softmax attention over the KV pool (``left``) and decayed linear
+    attention over a state slot (``right``); each output is RMS-normed over the model width with its own weight and
+    the two are averaged."""
+
+    left: BlockAttentionSpec
+    right: DecayAttentionSpec
+
+    def validate(self) -> None:
+        self.left.validate()
+        self.right.validate()
+
+    @property
+    def cache_row_width(self) -> int:
+        return self.left.cache_row_width
+
+    @property
+    def state_shape(self) -> tuple[int, ...]:
+        return self.right.state_shape
+
+    conv_tail_shape = None
+
+
+@dataclass(frozen=True)
 class DenseMlpSpec:
     ff: int
-    activation: str = "relu2"                          # "relu2" | "gelu" | "gelu_tanh"
+    activation: str = "relu2"                          # "relu2" | "gelu" | "gelu_tanh"; gated: "silu"
     kind: str = "dense"                                # key of executor.layered_decoder.FEED_FORWARDS
+    gated: bool = False                                # W_down (act(W_gate h) * (W_up h)) instead of W_down act(W_up h)
 
 
 @dataclass(frozen=True)
@@ -191,7 +323,7 @@ class MoeMlpSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     kind: str                                          # key of executor.layered_decoder.MIXERS
-    mixer: Mamba2Spec | SinkAttentionSpec | LatentAttentionSpec
+    mixer: "Mamba2Spec | SinkAttentionSpec | LatentAttentionSpec | MinGruSpec | RgLruSpec | SideBySideSpec"
     mlp: DenseMlpSpec | MoeMlpSpec | None = None
     weights_of: int | None = None                      # the layer whose tensors this one uses (cache / state are its own)
 
@@ -211,6 +343,14 @@ class LayeredConfig:
     learned_positions: bool = True
     embed_scale: float = 1.0
     logit_softcap: float = 0.0
+    # parallel blocks: x <- x + mixer(norm1(x)) + ff(norm2(x)), both norms of the same x (else the sublayers follow
+    # one another); embed_norm: the embedding passes the model's norm; token_side_dim > 0: after the block every layer
+    # adds a gated low-rank input looked up by the token id; depth_average: the next layer (and the output) reads a
+    # learned weighted sum of the embedding output and every layer result so far
+    parallel_block: bool = False
+    embed_norm: bool = False
+    token_side_dim: int = 0
+    depth_average: bool = False
 
     @property
     def num_layers(self) -> int:
@@ -221,7 +361,8 @@ class LayeredConfig:
         return [i for i, l in enumerate(self.layers) if hasattr(l.mixer, "cache_row_width")]
 
     def recurrent_layers(self) -> list[int]:
-        return [i for i, l in enumerate(self.layers) if isinstance(l.mixer, Mamba2Spec)]
+        """Layers that keep a fixed-size state per request slot (their mixer spec names its shape)."""
+        return [i for i, l in enumerate(self.layers) if hasattr(l.mixer, "state_shape")]
 
     def validate(self) -> None:
         for i, l in enumerate(self.layers):

@@ -1,6 +1,7 @@
 """Fixed-slot store for recurrent mixers, the counterpart of the KV pool for layers whose memory does not grow
-with the sequence: per recurrent layer one fp32 state tensor ``[slots, heads, state, head_dim]`` and one convolution
-tail ``[slots, taps - 1, channels]`` (the last inputs of the short convolution, in the activation dtype).
+with the sequence: per recurrent layer one fp32 state tensor ``[slots, *spec.state_shape]`` (a state-space or
+linear-attention memory ``heads x state x head_dim``, or one value per channel of an element-wise recurrence) and,
+for mixers with a short convolution, its tail ``[slots, taps - 1, channels]`` (the last inputs, in the activation dtype).
 
 A request holds one slot from admission to release; the same slot number indexes the request -> rows table of the
 KV pool (``ModelRunner.b_req_tokens_table``), as the reference's slot scheme does for attention
@@ -12,7 +13,7 @@ from __future__ import annotations
 
 import torch
 
-from .model_config import LayeredConfig, Mamba2Spec
+from .model_config import LayeredConfig
 
 
 class RecurrentStateManager:
@@ -23,9 +24,9 @@ class RecurrentStateManager:
         self.conv_tail: dict[int, torch.Tensor] = {}
         for i in config.recurrent_layers():
             m = config.layers[i].mixer
-            assert isinstance(m, Mamba2Spec)
-            self.ssm_state[i] = torch.zeros((num_slots, m.heads, m.state, m.head_dim), dtype=torch.float32, device=device)
-            self.conv_tail[i] = torch.zeros((num_slots, max(m.conv - 1, 1), m.conv_channels), dtype=dtype, device=device)
+            self.ssm_state[i] = torch.zeros((num_slots, *m.state_shape), dtype=torch.float32, device=device)
+            if m.conv_tail_shape is not None:
+                self.conv_tail[i] = torch.zeros((num_slots, *m.conv_tail_shape), dtype=dtype, device=device)
         self._free = list(range(num_slots - 1, -1, -1))
         self._held: set[int] = set()
 

@@ -10,9 +10,11 @@ from .flashdecoding import flash_decoding
 from .fused_moe import fused_moe, grouped_experts, moe_align_block_size, route_sigmoid_groups, route_topk
 from .latent import head_linear, latent_prepare, rope_heads, rope_table
 from .linear import linear, linear_simt
+from .parallel_stream import branch_sum_residual, depth_mix_norms, embed_rmsnorm, gelu_mul_gather
+from .rotary_heads import head_norm_rope_prepare, rope_table_freqs, rotary_frequencies
 from .residual_stream import embed_positions, gelu, post_norm_residual, relu_squared, rmsnorm_from_f32, softcap_to_f32
 from .sink_attention import attn_prepare, sink_attention
-from .ssm import causal_conv_silu, gated_group_norm, ssm_scan
+from .ssm import causal_conv_silu, gated_group_norm, gated_scan, norm_sigmoid_gate, ssm_scan
 from .rope_emb import rope_emb_forward, rope_emb_inplace, rope_kv_write
 from .sampling import argmax_rows
 from .skip_rmsnorm import can_fuse_int8_quant, skip_rmsnorm, skip_rmsnorm_quant_int8
@@ -46,6 +48,15 @@ __all__ = [
     "causal_conv_silu",
     "ssm_scan",
     "gated_group_norm",
+    "gated_scan",
+    "norm_sigmoid_gate",
+    "embed_rmsnorm",
+    "depth_mix_norms",
+    "branch_sum_residual",
+    "gelu_mul_gather",
+    "rope_table_freqs",
+    "rotary_frequencies",
+    "head_norm_rope_prepare",
     "argmax_rows",
     "rope_emb_forward",
     "rope_emb_inplace",

@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from ._common import check, dtype_code, lib, require_cuda, stream_handle
+from ._common import check, float_code, lib, require_cuda, stream_handle
 
 
 @torch.no_grad()
@@ -18,7 +18,7 @@ def swiglu_forward(a, b):
         a2 = a2.contiguous()
     if b2.stride(-1) != 1:
         b2 = b2.contiguous()
-    code = dtype_code(a2, "a")
+    code = float_code(a2, "a")
     c = torch.empty((a2.shape[0], n_cols), dtype=a.dtype, device=a.device)
     check(
         lib().b2l_swiglu(
