@@ -239,3 +239,93 @@ def forward(config: dict, tensors: dict, tokens: list[int], return_layers: bool 
     final = np.stack([norm_centred(v, f64(tensors["final.norm"]), eps) for v in x])
     logits = final @ f64(tensors["head"]).T
     return (logits, results) if return_layers else logits
+
+
+# ------------------------------------------------------------------------------------- configurations for tests #
+def attention_entry(heads=3, kv_heads=1, dim=8, vdim=10, rot_dims=4, base=10000.0, chunk=7, softcap=20.0,
+                    scaling="default", scale=None) -> dict:
+    if scaling == "default":
+        scaling = {"factor": 4.0, "fast": 32.0, "original": 64, "slow": 1.0}
+    rot = {"base": base, "dims": rot_dims}
+    if scaling:
+        rot["scaling"] = scaling
+    return {"dim": dim, "heads": heads, "kv_heads": kv_heads, "mask": {"size": chunk}, "rot": rot,
+            "scale": scale if scale is not None else 1.0 / math.sqrt(dim), "softcap": softcap, "vdim": vdim}
+
+
+def decay_entry(heads=2, dim=8, vdim=6, decay=(0.6, 0.97)) -> dict:
+    return {"decay": list(decay), "dim": dim, "heads": heads, "vdim": vdim}
+
+
+def layer_entry(kind: str, mixer: dict, ff: int | None = 12) -> dict:
+    return {"type": kind, "mixer": mixer, "mlp": {"ff": ff, "kind": "dense"} if ff else None}
+
+
+def parallel_layer(left: dict | None = None, right: dict | None = None, ff: int | None = 12) -> dict:
+    return layer_entry("parallel", {"left": left or attention_entry(), "right": right or decay_entry()}, ff)
+
+
+def mingru_layer(width=14, ff: int | None = 12) -> dict:
+    return layer_entry("mingru", {"width": width}, ff)
+
+
+def rglru_layer(width=12, blocks=3, conv=3, ff: int | None = 12) -> dict:
+    return layer_entry("rglru", {"blocks": blocks, "conv": conv, "width": width}, ff)
+
+
+def make_config(layers: list[dict], width=20, vocab=50, eps=1e-5, side_dim=3) -> dict:
+    return {"architecture": "Tisosun", "layers": layers, "norm": {"eps": eps}, "token_side": {"dim": side_dim},
+            "vocab": vocab, "width": width}
+
+
+def random_model(config: dict, seed: int = 0, spread: float = 1.0):
+    """Random tensors with checkpoint names, already rounded to bfloat16 values (returned as float32 torch tensors)."""
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    w, d = config["width"], config["token_side"]["dim"]
+    count = len(config["layers"])
+
+    def mat(rows, cols, gain=1.0):
+        return torch.randn(rows, cols, generator=g) * (gain * spread / math.sqrt(cols))
+
+    def vec(n, centre, dev):
+        return centre + dev * torch.randn(n, generator=g)
+
+    t = {"embed": torch.randn(config["vocab"], w, generator=g), "embed.norm": vec(w, 0.0, 0.2),
+         "side.embed": torch.randn(config["vocab"], d * count, generator=g), "final.norm": vec(w, 0.0, 0.2),
+         "head": mat(config["vocab"], w, 3.0)}
+    for i, layer in enumerate(config["layers"]):
+        p, m = f"l{i}.mix.", layer["mixer"]
+        t[f"l{i}.norm1"] = vec(w, 0.0, 0.2)
+        if layer["type"] == "mingru":
+            n = m["width"]
+            t.update({p + "z": mat(n, w, 2.0), p + "z.b": vec(n, 0.0, 0.5), p + "x": mat(n, w, 2.0), p + "x.b": vec(n, 0.0, 0.5),
+                      p + "g": mat(n, w, 2.0), p + "o": mat(w, n)})
+        elif layer["type"] == "rglru":
+            n, b = m["width"], m["blocks"]
+            per = n // b
+            t.update({p + "y": mat(n, w, 2.0), p + "y.b": vec(n, 0.0, 0.3), p + "x": mat(n, w, 2.0), p + "x.b": vec(n, 0.0, 0.3),
+                      p + "conv": 0.5 * torch.randn(n, m["conv"], generator=g), p + "conv.b": vec(n, 0.0, 0.2),
+                      p + "ra": torch.randn(b, per, per, generator=g) / math.sqrt(per), p + "ra.b": vec(b * per, 0.0, 0.5).view(b, per),
+                      p + "ri": torch.randn(b, per, per, generator=g) / math.sqrt(per), p + "ri.b": vec(b * per, 0.0, 0.5).view(b, per),
+                      p + "lam": vec(n, -2.0, 1.0), p + "o": mat(w, n)})
+        else:
+            L, R = m["left"], m["right"]
+            H, G, D, Dv = L["heads"], L["kv_heads"], L["dim"], L["vdim"]
+            t.update({p + "left.q": mat(H * D, w, 2.0), p + "left.q.b": vec(H * D, 0.0, 0.3), p + "left.k": mat(G * D, w, 2.0),
+                      p + "left.k.b": vec(G * D, 0.0, 0.3), p + "left.v": mat(G * Dv, w), p + "left.v.b": vec(G * Dv, 0.0, 0.3),
+                      p + "left.q.norm": vec(D, 1.0, 0.2), p + "left.k.norm": vec(D, 1.0, 0.2), p + "left.o": mat(w, H * Dv),
+                      p + "left.out": vec(w, 1.0, 0.2), p + "right.out": vec(w, 1.0, 0.2)})
+            h, dr, dv = R["heads"], R["dim"], R["vdim"]
+            t.update({p + "right.q": mat(h * dr, w, 2.0), p + "right.k": mat(h * dr, w, 2.0), p + "right.v": mat(h * dv, w, 2.0),
+                      p + "right.g": mat(h * dv, w, 2.0), p + "right.norm": vec(h * dv, 1.0, 0.2), p + "right.o": mat(w, h * dv)})
+        if layer["mlp"] is not None:
+            ff = layer["mlp"]["ff"]
+            t.update({f"l{i}.norm2": vec(w, 0.0, 0.2), f"l{i}.mlp.gate": mat(ff, w, 2.0), f"l{i}.mlp.up": mat(ff, w, 2.0),
+                      f"l{i}.mlp.down": mat(w, ff)})
+        mix = 0.2 * torch.randn(i + 2, generator=g)
+        mix[-1] += 0.8
+        t[f"l{i}.dwa"] = mix
+        t.update({f"l{i}.side.gate": mat(d, w, 2.0), f"l{i}.side.proj": mat(w, d), f"l{i}.side.norm": vec(w, 0.5, 0.1)})
+    return {k: v.to(torch.bfloat16).float() for k, v in t.items()}
