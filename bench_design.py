@@ -1,6 +1,7 @@
-"""``bench.py --design gufotar | pesivik``: prefill and decode throughput of a layer-list design at a few sizes that resemble
+"""``bench.py --design gufotar | pesivik | tisosun``: prefill and decode throughput of a layer-list design at a few sizes that resemble
 a real model's layers (random weights, synthetic ids), beside the closest existing model of the framework (the
-uniform rotary decoder: same width, layer count, attention geometry and feed-forward width), plus every kernel of the
+uniform rotary decoder: same width, layer count, attention geometry and feed-forward width; for Tisosun the Gufotar
+layer-list model, the other design with recurrent layers beside attention layers), plus every kernel of the
 new path timed alone against its like kernel with the fraction of the measured roofline each reaches.
 
 Timing: CUDA events on the launching stream, >= 3 warm-up runs, a 256 MiB write between timed runs (larger than the
@@ -66,11 +67,15 @@ def gufotar_config(sz: dict, max_positions: int) -> dict:
             "vocab": sz["vocab"], "width": sz["width"]}
 
 
-def build_gufotar(sz, batch, max_positions, dev, dtype):
+def build_gufotar(sz, batch, max_positions, dev, dtype, every_ff=False):
     from lite_llama_b200.executor import ModelRunner
     from lite_llama_b200.executor.layered_decoder import map_gufotar_weights, parse_gufotar_config, random_gufotar_tensors
 
-    conf = parse_gufotar_config(gufotar_config(sz, max_positions))
+    raw = gufotar_config(sz, max_positions)
+    if every_ff:                              # a feed-forward in every layer, as the designs it is compared with have
+        for layer in raw["layers"]:
+            layer["mlp"] = {"ff": sz["ff"], "kind": "dense"}
+    conf = parse_gufotar_config(raw)
     conf.validate()
     weights = map_gufotar_weights(conf, random_gufotar_tensors(conf, seed=0), dev, dtype)
     return ModelRunner(conf, weights, batch * max_positions, device=dev, dtype=dtype, max_requests=batch)
@@ -521,6 +526,256 @@ def pesivik_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) 
     return rows
 
 
+# ------------------------------------------------------------------------------------------------------ Tisosun #
+T_SIZES = {
+    # attention half: heads x head_dim on kv_heads, blocks of `chunk` positions; linear-attention half: r_heads memories
+    # of r_dim x r_vdim; recurrent layers of the model width; gated feed-forward; 64-wide token input
+    "small": dict(width=1024, layers=4, heads=16, kv_heads=4, head_dim=64, chunk=1024, r_heads=16, r_dim=64, r_vdim=64,
+                  ff=2048, side=64, vocab=32000, s_heads=32, s_dim=64, s_state=64, s_groups=4),
+    "1b": dict(width=2048, layers=8, heads=16, kv_heads=4, head_dim=128, chunk=1024, r_heads=16, r_dim=128, r_vdim=128,
+               ff=4096, side=64, vocab=32000, s_heads=64, s_dim=64, s_state=128, s_groups=8),
+    "8b": dict(width=4096, layers=8, heads=32, kv_heads=8, head_dim=128, chunk=1024, r_heads=32, r_dim=128, r_vdim=128,
+               ff=7168, side=64, vocab=32000, s_heads=128, s_dim=64, s_state=128, s_groups=8),
+}
+
+
+def tisosun_config(sz: dict) -> dict:
+    """Layers in the order parallel, real-gated LRU, parallel, minimal GRU, ... with a gated feed-forward each."""
+    par = {"type": "parallel", "mlp": {"ff": sz["ff"], "kind": "dense"},
+           "mixer": {"left": {"dim": sz["head_dim"], "heads": sz["heads"], "kv_heads": sz["kv_heads"],
+                              "mask": {"size": sz["chunk"]},
+                              "rot": {"base": 10000.0, "dims": sz["head_dim"] // 2,
+                                      "scaling": {"factor": 4.0, "fast": 32.0, "original": 4096, "slow": 1.0}},
+                              "scale": 1.0 / math.sqrt(sz["head_dim"]), "softcap": 30.0, "vdim": sz["head_dim"]},
+                     "right": {"decay": [1.0 - 2.0 ** (-2 - 6 * h / sz["r_heads"]) for h in range(sz["r_heads"])],
+                               "dim": sz["r_dim"], "heads": sz["r_heads"], "vdim": sz["r_vdim"]}}}
+    lru = {"type": "rglru", "mlp": {"ff": sz["ff"], "kind": "dense"},
+           "mixer": {"blocks": sz["heads"], "conv": 4, "width": sz["width"]}}
+    gru = {"type": "mingru", "mlp": {"ff": sz["ff"], "kind": "dense"}, "mixer": {"width": sz["width"]}}
+    order = [par, lru, par, gru]
+    return {"architecture": "Tisosun", "layers": [dict(order[i % 4]) for i in range(sz["layers"])], "norm": {"eps": 1e-6},
+            "token_side": {"dim": sz["side"]}, "vocab": sz["vocab"], "width": sz["width"]}
+
+
+def build_tisosun(sz, batch, max_positions, dev, dtype):
+    from lite_llama_b200.executor import ModelRunner
+    from lite_llama_b200.executor.layered_decoder import map_tisosun_weights, parse_tisosun_config, random_tisosun_tensors
+
+    conf = parse_tisosun_config(tisosun_config(sz))
+    conf.validate()
+    weights = map_tisosun_weights(conf, random_tisosun_tensors(conf, seed=0), dev, dtype)
+    return ModelRunner(conf, weights, batch * max_positions, device=dev, dtype=dtype, max_requests=batch)
+
+
+def tisosun_step_throughput(sz, batch, prompt, dev, dtype, flush) -> dict:
+    """tokens/s of a whole-prompt step and of a decode step: Tisosun beside the Gufotar layer-list model of the same
+    width, depth, attention geometry and feed-forward width (its feed-forward in every layer here; ungated, so the
+    gated one of Tisosun is given 2/3 of its width: equal feed-forward weights)."""
+    max_pos = prompt + 64
+    out = {}
+    gen = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, sz["vocab"], (batch, prompt), generator=gen)
+    tok = [[int(t)] for t in torch.randint(0, sz["vocab"], (batch,), generator=gen)]
+    like = dict(sz, ff=sz["ff"] * 3 // 2)
+    for name, build in (("tisosun", lambda: build_tisosun(sz, batch, max_pos, dev, dtype)),
+                        ("gufotar", lambda: build_gufotar(like, batch, max_pos, dev, dtype, every_ff=True))):
+        r = build()
+        r.enable_ragged_decode_graphs(widths=(batch,), ctx_buckets=(max_pos,))
+        reqs = []
+
+        def prefill():
+            for q in reqs:
+                r.close_request(q)
+            reqs[:] = [r.open_request() for _ in range(batch)]
+            return r.forward_ragged([(q, ids[i].tolist()) for i, q in enumerate(reqs)])
+
+        pre = timed(prefill, flush, warmup=2, reps=3)
+        state = {"n": 0}
+
+        def decode():
+            if state["n"] >= 48:
+                prefill()
+                state["n"] = 0
+            state["n"] += 1
+            return r.forward_ragged([(q, tok[i]) for i, q in enumerate(reqs)])
+
+        dec = timed(decode, flush, warmup=3, reps=9)
+        out[name] = {"prefill_ms": pre, "prefill_tok_s": batch * prompt / pre * 1e3, "decode_ms": dec,
+                     "decode_tok_s": batch / dec * 1e3, "weight_bytes_per_step": r.model.w.nbytes_per_step()}
+        del r, reqs, prefill, decode
+        gc.collect()
+        torch.cuda.empty_cache()
+    return out
+
+
+def tisosun_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) -> list[dict]:
+    """Every kernel of the Tisosun path alone at the size's shapes beside its like kernel of the Gufotar path (the
+    closest existing model), with the fraction of the measured roofline each reaches."""
+    import lite_llama_b200.kernels as K
+
+    es = 2
+    W, H, G, D, ff, side = sz["width"], sz["heads"], sz["kv_heads"], sz["head_dim"], sz["ff"], sz["side"]
+    RH, RD, RV, chunk = sz["r_heads"], sz["r_dim"], sz["r_vdim"], sz["chunk"]
+    SH, SP, SN, SG = sz["s_heads"], sz["s_dim"], sz["s_state"], sz["s_groups"]
+    T, ctx, levels = batch * prompt, prompt, sz["layers"] // 2 + 1
+    rows: list[dict] = []
+
+    def i32(v):
+        return torch.tensor(list(v), dtype=torch.int32, device=dev)
+
+    def rnd(*shape, dt=dtype, s=1.0):
+        return (torch.randn(*shape, device=dev) * s).to(dt)
+
+    def add(name, like, fn, nbytes=0, flops=0, like_fn=None, like_bytes=None, like_flops=None):
+        ms = timed(fn, flush)
+        row = {"kernel": name, "us": ms * 1e3}
+        if flops:
+            row.update(tflops=flops / ms / 1e9, frac=flops / ms / 1e9 / tflops, bound="tensor")
+        else:
+            row.update(gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / hbm_gbs, bound="hbm")
+        if like_fn is not None:
+            lms = timed(like_fn, flush)
+            lf = like_flops if like_flops is not None else flops
+            lb = like_bytes if like_bytes is not None else nbytes
+            lfrac = lf / lms / 1e9 / tflops if flops else lb / lms / 1e6 / hbm_gbs
+            row.update(like=like, like_us=lms * 1e3, like_frac=lfrac,
+                       distance_ratio=(lfrac / row["frac"]) if row["frac"] else None)
+        rows.append(row)
+
+    p_start, p_ctx, p_slot = i32(range(0, T + 1, prompt)), i32([0] * batch), i32(range(batch))
+    d_start, d_ctx = i32(range(batch + 1)), i32([ctx] * batch)
+    toks = torch.randint(0, sz["vocab"], (T,), device=dev, dtype=torch.int32)
+    pos_p = i32(list(range(prompt)) * batch)
+    # ---------------- residual stack
+    embed, wn = rnd(sz["vocab"], W), rnd(W, s=0.1)
+    stack = torch.randn(levels + 1, T, W, device=dev)
+    add("embed_rmsnorm", "embed_positions", lambda: K.embed_rmsnorm(toks, embed, wn, 1e-6, out=stack[0]),
+        nbytes=T * W * (es + 4), like_fn=lambda: K.embed_positions(toks, pos_p, embed, None), like_bytes=T * W * (es + 4 + es))
+    coef, w1, w2 = rnd(levels, s=0.3), rnd(W, s=0.1), rnd(W, s=0.1)
+    y = rnd(T, W)
+    resid = torch.randn(T, W, device=dev)
+    like_norm = lambda: K.post_norm_residual(resid, y, wn, 1e-5)
+    like_norm_bytes = T * W * (4 + 4 + es + es)
+    add("depth_mix_norms (%d levels -> next level + two input norms)" % levels, "post_norm_residual",
+        lambda: K.depth_mix_norms(stack[:levels], levels, coef, w1, w2, 1e-6, out=stack[levels]),
+        nbytes=T * W * (4 * levels + 4 + 2 * es), like_fn=like_norm, like_bytes=like_norm_bytes)
+    a, b, c = rnd(T, W), rnd(T, W), rnd(T, W)
+    add("branch_sum_residual (two normed branches + feed-forward)", "post_norm_residual",
+        lambda: K.branch_sum_residual(resid, a, w1, b, w2, c, 1e-6, 0.5), nbytes=T * W * (4 + 4 + 3 * es + es),
+        like_fn=like_norm, like_bytes=like_norm_bytes)
+    z, table = rnd(T, side), rnd(sz["vocab"], side * sz["layers"])
+    up = rnd(T, ff)
+    add("gelu_mul_gather (token input)", "relu_squared", lambda: K.gelu_mul_gather(z, toks, table, side),
+        nbytes=T * side * 3 * es, like_fn=lambda: K.relu_squared(up), like_bytes=T * ff * 2 * es)
+    gu = rnd(T, 2 * ff)
+    add("swiglu_forward (gated feed-forward)", "relu_squared", lambda: K.swiglu_forward(gu[:, :ff], gu[:, ff:]),
+        nbytes=T * ff * 3 * es, like_fn=lambda: K.relu_squared(up), like_bytes=T * ff * 2 * es)
+    # ---------------- attention half
+    kvw = G * 2 * D
+    pool = rnd(batch * (ctx + 1), kvw, s=0.5)
+    tab = torch.arange(batch * (ctx + 1), dtype=torch.int32, device=dev).view(batch, ctx + 1)
+    qkv = rnd(T, (H + 2 * G) * D, s=0.5)
+    rows_p = tab[:, :ctx].reshape(-1).contiguous()
+    rot = D // 2
+    f, mag = K.rotary_frequencies(rot, 10000.0, 4.0, 4096.0, 32.0, 1.0)
+    freqs = torch.tensor(f, dtype=torch.float32, device=dev)
+    cs = K.rope_table_freqs(pos_p, freqs, mag)
+    add("rope_table_freqs (once per step)", "rope_table", lambda: K.rope_table_freqs(pos_p, freqs, mag),
+        nbytes=T * (4 + rot * 4), like_fn=lambda: K.rope_table(pos_p, rot, 10000.0))
+    qn, kn = rnd(D, s=0.1) + 1, rnd(D, s=0.1) + 1
+    qw, kw = rnd(H * D, s=0.1) + 1, rnd(G * D, s=0.1) + 1
+    prep_bytes = T * ((2 * H + 2 * G) * D * es + 2 * G * D * es)
+    add("head_norm_rope_prepare", "attn_prepare",
+        lambda: K.head_norm_rope_prepare(qkv, pool, rows_p, cs, qn, kn, H, G, D, D, rot, 1e-6), nbytes=prep_bytes + T * rot * 4,
+        like_fn=lambda: K.attn_prepare(qkv, pool, rows_p, pos_p, H * D, G * D, G * D, qw, kw, 1e-5, 0.5, 64.0),
+        like_bytes=prep_bytes)
+    out = torch.empty(T, H * D, dtype=dtype, device=dev)
+    scale = 1.0 / math.sqrt(D)
+    sink = rnd(H)
+    seen = sum(t % chunk + 1 for t in range(prompt))
+    add("block-masked attention (prompts, blocks of %d)" % chunk, "sink_attention (full causal, sink)",
+        lambda: K.sink_attention(out, qkv, pool, tab, p_start, p_ctx, p_slot, None, batch, prompt, None, H, G, D, D, scale, 30.0,
+                                 block=chunk),
+        flops=4 * batch * H * D * seen,
+        like_fn=lambda: K.sink_attention(out, qkv, pool, tab, p_start, p_ctx, p_slot, None, batch, prompt, sink, H, G, D, D, scale, 30.0),
+        like_flops=4 * batch * H * D * prompt * (prompt + 1) / 2)
+    keys = min(ctx + 1, ctx % chunk + 1)
+    splits = max(1, min(128, -(-min(ctx + 1, chunk) // 128)))
+    per = -(-(-(-min(ctx + 1, chunk) // splits)) // 32) * 32
+    fs = max(1, min(128, -(-(ctx + 1) // 128)))
+    fper = -(-(-(-(ctx + 1) // fs)) // 32) * 32
+    add("block-masked attention (decode, %d of %d keys seen)" % (keys, ctx + 1), "sink_attention (decode, all keys)",
+        lambda: K.sink_attention(out, qkv, pool, tab, d_start, d_ctx, p_slot, None, batch, 1, None, H, G, D, D, scale, 30.0,
+                                 num_splits=splits, split_keys=per, block=chunk),
+        nbytes=batch * keys * kvw * es,
+        like_fn=lambda: K.sink_attention(out, qkv, pool, tab, d_start, d_ctx, p_slot, None, batch, 1, sink, H, G, D, D, scale, 30.0,
+                                         num_splits=fs, split_keys=fper),
+        like_bytes=batch * (ctx + 1) * kvw * es)
+    # ---------------- linear-attention half beside the state-space scan
+    rin = RH * RV
+    rproj = rnd(T, 2 * rin + 2 * RH * RD, s=0.5)
+    dec = torch.tensor([1.0 - 2.0 ** (-2 - 6 * h / RH) for h in range(RH)], dtype=torch.float32, device=dev)
+    rst = torch.zeros(batch, RH, RD, RV, device=dev)
+    inner, gn = SH * SP, SG * SN
+    xbc = rnd(T, inner + 2 * gn, s=0.5)
+    sproj = rnd(T, SH)
+    dtb, alog, dsk = rnd(SH), rnd(SH, s=0.5), rnd(SH)
+    sst = torch.zeros(batch, SH, SN, SP, device=dev)
+    xr = rproj[:, :rin + 2 * RH * RD]
+    add("ssm_scan, fixed decay (prompts)", "ssm_scan (state-space, prompts)",
+        lambda: K.ssm_scan(xr, None, None, None, None, rst, p_start, p_ctx, p_slot, RH, RH, RD, RV, fixed_decay=dec, silu_inputs=True),
+        nbytes=T * ((rin + 2 * RH * RD) * es + rin * 4) + batch * RH * RD * RV * 4,
+        like_fn=lambda: K.ssm_scan(xbc, sproj, dtb, alog, dsk, sst, p_start, p_ctx, p_slot, SH, SG, SN, SP),
+        like_bytes=T * ((inner + 2 * gn) * es + SH * es + inner * 4) + batch * SH * SP * SN * 4)
+    add("ssm_scan, fixed decay (decode)", "ssm_scan (state-space, decode)",
+        lambda: K.ssm_scan(xr[:batch], None, None, None, None, rst, d_start, d_ctx, p_slot, RH, RH, RD, RV, fixed_decay=dec, silu_inputs=True),
+        nbytes=batch * RH * RD * RV * 8,
+        like_fn=lambda: K.ssm_scan(xbc[:batch], sproj[:batch], dtb, alog, dsk, sst, d_start, d_ctx, p_slot, SH, SG, SN, SP),
+        like_bytes=batch * SH * SP * SN * 8)
+    yf = torch.randn(T, rin, device=dev)
+    yg = torch.randn(T, inner, device=dev)
+    nw, gw = rnd(rin, s=0.1) + 1, rnd(inner, s=0.1) + 1
+    zz = rnd(T, inner)
+    add("norm_sigmoid_gate", "gated_group_norm", lambda: K.norm_sigmoid_gate(yf, rproj[:, rin + 2 * RH * RD:], nw, 1e-6),
+        nbytes=T * rin * (4 + es + es), like_fn=lambda: K.gated_group_norm(yg, zz, gw, SG, 1e-5), like_bytes=T * inner * (4 + es + es))
+    # ---------------- element-wise recurrences
+    gproj = rnd(T, 3 * W)
+    gst = torch.zeros(batch, W, device=dev)
+    scan_like = lambda: K.ssm_scan(xbc, sproj, dtb, alog, dsk, sst, p_start, p_ctx, p_slot, SH, SG, SN, SP)
+    scan_like_bytes = T * ((inner + 2 * gn) * es + SH * es + inner * 4) + batch * SH * SP * SN * 4
+    add("gated_scan, minimal GRU (prompts)", "ssm_scan (state-space, prompts)",
+        lambda: K.gated_scan("mingru", gst, gproj[:, :W], gproj[:, W:2 * W], gproj[:, 2 * W:], p_start, p_ctx, p_slot),
+        nbytes=T * W * 4 * es, like_fn=scan_like, like_bytes=scan_like_bytes)
+    add("gated_scan, minimal GRU (decode)", "ssm_scan (state-space, decode)",
+        lambda: K.gated_scan("mingru", gst, gproj[:batch, :W], gproj[:batch, W:2 * W], gproj[:batch, 2 * W:], d_start, d_ctx, p_slot),
+        nbytes=batch * W * (4 * es + 8),
+        like_fn=lambda: K.ssm_scan(xbc[:batch], sproj[:batch], dtb, alog, dsk, sst, d_start, d_ctx, p_slot, SH, SG, SN, SP),
+        like_bytes=batch * SH * SP * SN * 8)
+    lproj = rnd(T, 2 * W)
+    cw, cb = rnd(W, 4, s=0.5), rnd(W, s=0.1)
+    tail = torch.zeros(batch, 3, W, dtype=dtype, device=dev)
+    gcw, gcb = rnd(inner + 2 * gn, 4, s=0.5), rnd(inner + 2 * gn, s=0.1)
+    gtail = torch.zeros(batch, 3, inner + 2 * gn, dtype=dtype, device=dev)
+    gp = rnd(T, 2 * inner + 2 * gn + SH)
+    add("causal convolution without activation (prompts)", "causal_conv_silu",
+        lambda: K.causal_conv_silu(lproj, W, W, cw, cb, tail, p_start, p_ctx, p_slot, activation=False), nbytes=T * W * 2 * es,
+        like_fn=lambda: K.causal_conv_silu(gp, inner, inner + 2 * gn, gcw, gcb, gtail, p_start, p_ctx, p_slot),
+        like_bytes=T * (inner + 2 * gn) * 2 * es)
+    u = rnd(T, W, s=0.5)
+    per_b = W // H
+    gw2 = rnd(H, per_b, per_b, s=0.1)
+    gates = torch.empty(T, 2 * W, dtype=dtype, device=dev)
+    dx, dw = rnd(T, per_b), rnd(W, per_b, s=0.1)
+    add("head_linear (block-diagonal gate projection)", "linear (one GEMM of equal FLOPs)",
+        lambda: K.head_linear(gates[:, :W], per_b, u, per_b, gw2), flops=2 * T * W * per_b, like_fn=lambda: K.linear(dx, dw))
+    br, bi, lam = rnd(W, s=0.3), rnd(W, s=0.3), rnd(W) - 2
+    add("gated_scan, real-gated LRU (prompts)", "ssm_scan (state-space, prompts)",
+        lambda: K.gated_scan("rglru", gst, u, gates[:, :W], gates[:, W:], p_start, p_ctx, p_slot, p3=lproj[:, :W], bias_r=br,
+                             bias_i=bi, lam=lam, decay_scale=8.0),
+        nbytes=T * W * 5 * es, like_fn=scan_like, like_bytes=scan_like_bytes)
+    return rows
+
+
 def run(args) -> None:
     from bench import ClockSampler, peaks
 
@@ -530,8 +785,9 @@ def run(args) -> None:
     hbm_gbs, tflops, src = peaks()
     flush = _flush_buffer(dev)
     sizes = [s for s in (args.design_sizes or "small,1b,8b").split(",") if s]
-    table, steps, kernels = ((P_SIZES, pesivik_step_throughput, pesivik_kernel_table) if args.design == "pesivik"
-                             else (SIZES, step_throughput, kernel_table))
+    table, steps, kernels = {"pesivik": (P_SIZES, pesivik_step_throughput, pesivik_kernel_table),
+                             "tisosun": (T_SIZES, tisosun_step_throughput, tisosun_kernel_table)}.get(
+        args.design, (SIZES, step_throughput, kernel_table))
     result = {"design": args.design, "dtype": "bf16", "data": "synthetic ids, random weights", "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": tflops, "source": src},
               "batch": args.batch, "prompt_len": args.prompt_len, "l2_policy": "256 MiB written between timed runs", "sizes": {}}
     t0 = time.time()

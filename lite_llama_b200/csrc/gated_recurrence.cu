@@ -18,6 +18,7 @@
 //   norm_sigmoid_gate   o = unit_rms(y) * w * sigmoid(z)   (y fp32 rows, z a column view in T; the gate acts AFTER
 //                       the norm, unlike gated_group_norm)
 #include "common.cuh"
+#include "rowvec.cuh"
 
 namespace {
 
@@ -127,13 +128,20 @@ __global__ void __launch_bounds__(kWarps * 32) gated_scan_kernel(ScanArgs k) {
 template <typename T>
 __global__ void __launch_bounds__(256) norm_sigmoid_gate_kernel(T* __restrict__ o, const float* __restrict__ y,
                                                                 const T* __restrict__ z, int64_t zs,
-                                                                const T* __restrict__ w, int n, float eps) {
+                                                                const T* __restrict__ w, int n, float eps, int vec) {
   pdl_prologue();
   __shared__ float red[32];
   const int64_t t = blockIdx.x;
   const float* yr = y + t * n;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(yr[i], yr[i], ss);
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(yr + i);
+      ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(yr[i], yr[i], ss);
+  }
   ss = warp_reduce_sum(ss);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   if (lane == 0) red[warp] = ss;
@@ -141,6 +149,18 @@ __global__ void __launch_bounds__(256) norm_sigmoid_gate_kernel(T* __restrict__ 
   float tot = lane < nw ? red[lane] : 0.f;
   tot = warp_reduce_sum(tot);
   const float rstd = 1.0f / sqrtf(tot / (float)n + eps);
+  if (vec) {                                   // the row is read again from L1
+    for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+      float v[4], g[4], q[4];
+      row_load4(yr + i, v);
+      row_load4(w + i, g);
+      row_load4(z + t * zs + i, q);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) v[c] = v[c] * rstd * g[c] * sigmoid_f(q[c]);
+      row_store4(o + t * (int64_t)n + i, v);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < n; i += blockDim.x)
     o[t * n + i] = from_f32<T>(yr[i] * rstd * to_f32(w[i]) * sigmoid_f(to_f32(z[t * zs + i])));
 }
@@ -186,7 +206,9 @@ extern "C" int b2l_norm_sigmoid_gate(void* out, const void* y_f32, const void* z
   const int threads = n >= 1024 ? 256 : (n >= 256 ? 128 : 64);
   B2L_DISPATCH_FLOAT(dtype, "norm_sigmoid_gate", {
     b2l_launch(norm_sigmoid_gate_kernel<T>, dim3((unsigned)rows), dim3(threads), (size_t)0, st, (T*)out,
-               (const float*)y_f32, (const T*)z, z_row_stride, (const T*)weight, n, eps);
+               (const float*)y_f32, (const T*)z, z_row_stride, (const T*)weight, n, eps,
+               (int)(n % 4 == 0 && z_row_stride % 4 == 0 && (uintptr_t)y_f32 % 16 == 0 && row_aligned4<T>(z) &&
+                     row_aligned4<T>(weight) && row_aligned4<T>(out)));
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;

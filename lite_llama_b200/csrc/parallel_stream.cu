@@ -10,6 +10,7 @@
 //   * gelu_mul_gather       o[t, d] = gelu_tanh(z[t, d]) * table[token[t], col0 + d]       (per-layer token input)
 // unit_rms(v) = v / sqrt(mean(v^2) + eps).  All statistics, sums and the stack itself are fp32.
 #include "common.cuh"
+#include "rowvec.cuh"
 
 namespace {
 
@@ -31,7 +32,7 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 template <typename T>
 __global__ void embed_rmsnorm_kernel(float* __restrict__ r, const int* __restrict__ tokens, const T* __restrict__ embed,
                                      const T* __restrict__ w, int64_t n, int64_t vocab, float eps, float offset,
-                                     float scale) {
+                                     float scale, int vec) {
   pdl_prologue();
   __shared__ float red[32];
   const int64_t t = blockIdx.x;
@@ -39,6 +40,24 @@ __global__ void embed_rmsnorm_kernel(float* __restrict__ r, const int* __restric
   tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);        // ids are validated on the host; never read outside
   const T* e = embed + tok * n;
   float ss = 0.f;
+  if (vec) {                                   // 4 elements per access; the second pass finds the row in L1
+    for (int64_t i = (int64_t)threadIdx.x * 4; i < n; i += (int64_t)blockDim.x * 4) {
+      float v[4];
+      row_load4(e + i, v);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) { v[c] *= scale; ss = fmaf(v[c], v[c], ss); }
+    }
+    const float rstd = 1.0f / sqrtf(block_sum_ps(ss, red) / (float)n + eps);
+    for (int64_t i = (int64_t)threadIdx.x * 4; i < n; i += (int64_t)blockDim.x * 4) {
+      float v[4], g[4] = {0.f, 0.f, 0.f, 0.f};
+      row_load4(e + i, v);
+      if (w) row_load4(w + i, g);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) v[c] = v[c] * scale * rstd * (w ? offset + g[c] : 1.0f);
+      row_store4(r + t * n + i, v);
+    }
+    return;
+  }
   for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_f32(e[i]) * scale; ss = fmaf(v, v, ss); }
   const float rstd = 1.0f / sqrtf(block_sum_ps(ss, red) / (float)n + eps);
   for (int64_t i = threadIdx.x; i < n; i += blockDim.x)
@@ -94,11 +113,18 @@ __global__ void __launch_bounds__(256) depth_mix_norms_kernel(float* __restrict_
     for (int k = 0; k < NV; ++k) {
       const int64_t i = (int64_t)(k * 256 + threadIdx.x) * 4;
       if (i >= n) continue;
+      float g[4], o[4];
+      if (h1) {
+        row_load4(w1 + i, g);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const float u = v[k][c] * rstd;
-        if (h1) h1[t * n + i + c] = from_f32<T>(u * (offset + to_f32(w1[i + c])));
-        if (h2) h2[t * n + i + c] = from_f32<T>(u * (offset + to_f32(w2[i + c])));
+        for (int c = 0; c < 4; ++c) o[c] = v[k][c] * rstd * (offset + g[c]);
+        row_store4(h1 + t * n + i, o);
+      }
+      if (h2) {
+        row_load4(w2 + i, g);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[c] = v[k][c] * rstd * (offset + g[c]);
+        row_store4(h2 + t * n + i, o);
       }
     }
   } else {
@@ -129,7 +155,7 @@ __global__ void __launch_bounds__(256) branch_sum_residual_kernel(float* __restr
                                                                   const T* __restrict__ wa, const T* __restrict__ b,
                                                                   int64_t bs, const T* __restrict__ wb,
                                                                   const T* __restrict__ c, int64_t cs, int64_t n,
-                                                                  float eps, float scale) {
+                                                                  float eps, float scale, int vec) {
   pdl_prologue();
   __shared__ float red[32];
   const int64_t t = blockIdx.x;
@@ -137,6 +163,60 @@ __global__ void __launch_bounds__(256) branch_sum_residual_kernel(float* __restr
   const T* br = b ? b + t * bs : nullptr;
   const T* cr = c ? c + t * cs : nullptr;
   float ra = 1.f, rb = 1.f;
+  if (vec) {
+    // 4 elements per access: statistics first (the branches are read again from L1 in the second pass)
+    if (wa || (br && wb)) {
+      float sa = 0.f, sb = 0.f;
+      for (int64_t i = (int64_t)threadIdx.x * 4; i < n; i += (int64_t)blockDim.x * 4) {
+        float v[4];
+        if (wa) {
+          row_load4(ar + i, v);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) sa = fmaf(v[k], v[k], sa);
+        }
+        if (br && wb) {
+          row_load4(br + i, v);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) sb = fmaf(v[k], v[k], sb);
+        }
+      }
+      if (wa) ra = 1.0f / sqrtf(block_sum_ps(sa, red) / (float)n + eps);
+      if (br && wb) rb = 1.0f / sqrtf(block_sum_ps(sb, red) / (float)n + eps);
+    }
+    for (int64_t i = (int64_t)threadIdx.x * 4; i < n; i += (int64_t)blockDim.x * 4) {
+      float m[4], g[4], x[4];
+      row_load4(ar + i, m);
+      if (wa) {
+        row_load4(wa + i, g);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) m[k] = m[k] * ra * g[k];
+      }
+      if (br) {
+        row_load4(br + i, x);
+        if (wb) {
+          row_load4(wb + i, g);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) m[k] += x[k] * rb * g[k];
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) m[k] += x[k];
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) m[k] *= scale;
+      if (cr) {
+        row_load4(cr + i, x);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) m[k] += x[k];
+      }
+      row_load4(r + t * n + i, x);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) m[k] += x[k];
+      row_store4(r + t * n + i, m);
+      if (act) row_store4(act + t * n + i, m);
+    }
+    return;
+  }
   if (wa) {
     float ss = 0.f;
     for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_f32(ar[i]); ss = fmaf(v, v, ss); }
@@ -188,7 +268,8 @@ extern "C" int b2l_embed_rmsnorm(void* residual_f32, const void* tokens_i32, con
   cudaStream_t st = (cudaStream_t)stream;
   B2L_DISPATCH_FLOAT(dtype, "embed_rmsnorm", {
     b2l_launch(embed_rmsnorm_kernel<T>, dim3((unsigned)rows), dim3(256), (size_t)0, st, (float*)residual_f32,
-               (const int*)tokens_i32, (const T*)embed, (const T*)weight, n, vocab, eps, weight_offset, scale);
+               (const int*)tokens_i32, (const T*)embed, (const T*)weight, n, vocab, eps, weight_offset, scale,
+               (int)(n % 4 == 0 && row_aligned4<T>(embed) && row_aligned4<T>(weight) && (uintptr_t)residual_f32 % 16 == 0));
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;
@@ -202,8 +283,11 @@ extern "C" int b2l_depth_mix_norms(void* x_out_f32, void* h1, void* h2, const vo
   B2L_REQUIRE(rows >= 0 && n > 0, "depth_mix_norms: bad shape");
   if (rows == 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const bool fast = n % 4 == 0 && n <= 8192 && level_stride % 4 == 0 && (uintptr_t)stack_f32 % 16 == 0 &&
-                    (x_out_f32 == nullptr || (uintptr_t)x_out_f32 % 16 == 0);
+  bool fast = n % 4 == 0 && n <= 8192 && level_stride % 4 == 0 && (uintptr_t)stack_f32 % 16 == 0 &&
+              (x_out_f32 == nullptr || (uintptr_t)x_out_f32 % 16 == 0);
+  B2L_DISPATCH_FLOAT(dtype, "depth_mix_norms", {
+    fast = fast && row_aligned4<T>(h1) && row_aligned4<T>(h2) && row_aligned4<T>(w1) && row_aligned4<T>(w2);
+  });
   B2L_REQUIRE(fast || x_out_f32, "depth_mix_norms: rows of %lld elements need the mixed output buffer", (long long)n);
 #define B2L_DMN(NVV)                                                                                                \
   b2l_launch(depth_mix_norms_kernel<T, NVV>, dim3((unsigned)rows), dim3(256), (size_t)0, st, (float*)x_out_f32,    \
@@ -232,7 +316,10 @@ extern "C" int b2l_branch_sum_residual(void* residual_f32, void* act, const void
   B2L_DISPATCH_FLOAT(dtype, "branch_sum_residual", {
     b2l_launch(branch_sum_residual_kernel<T>, dim3((unsigned)rows), dim3(256), (size_t)0, st, (float*)residual_f32,
                (T*)act, (const T*)a, a_row_stride, (const T*)a_weight, (const T*)b, b_row_stride, (const T*)b_weight,
-               (const T*)c, c_row_stride, n, eps, scale);
+               (const T*)c, c_row_stride, n, eps, scale,
+               (int)(n % 4 == 0 && a_row_stride % 4 == 0 && b_row_stride % 4 == 0 && c_row_stride % 4 == 0 &&
+                     row_aligned4<T>(a) && row_aligned4<T>(b) && row_aligned4<T>(c) && row_aligned4<T>(a_weight) &&
+                     row_aligned4<T>(b_weight) && row_aligned4<T>(act) && (uintptr_t)residual_f32 % 16 == 0));
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;

@@ -9,6 +9,7 @@
 //                              go to pool row kv_rows[t] = [k heads | v heads].
 // Statistics, angles and the rotation are fp32; one rounding to T at the end.
 #include "common.cuh"
+#include "rowvec.cuh"
 
 namespace {
 
@@ -76,6 +77,76 @@ __global__ void __launch_bounds__(kPrepWarps * 32) head_norm_rope_prepare_kernel
   for (int i = threadIdx.x; i < G * Dv; i += blockDim.x) vout[i] = vin[i];
 }
 
+// The same for the neighbour pairing with 4 elements per access: head_dim a multiple of 4 and at most C * 128, every
+// row and head start aligned to 4 elements.  A lane's 4 elements hold two whole pairs, so the head never leaves the
+// registers: one read and one write per element.
+constexpr int kVecWarps = 8;
+
+template <typename T, int C>
+__global__ void __launch_bounds__(kVecWarps * 32) head_norm_rope_prepare_vec_kernel(
+    T* __restrict__ qkv, int64_t qkv_stride, T* __restrict__ pool, int64_t pool_stride, const int* __restrict__ kv_rows,
+    const float* __restrict__ cos_sin, const T* __restrict__ q_w, const T* __restrict__ k_w, int H, int G, int D,
+    int Dv, int rot_dims, float eps) {
+  pdl_prologue();
+  const int64_t t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  T* src = qkv + t * qkv_stride;
+  T* dst_pool = pool + (int64_t)kv_rows[t] * pool_stride;
+  const int half = rot_dims / 2;
+  const float* cs = cos_sin ? cos_sin + t * rot_dims : nullptr;
+  for (int h = warp; h < H + G; h += kVecWarps) {
+    const bool is_q = h < H;
+    const T* in = src + (int64_t)h * D;
+    const T* w = is_q ? q_w : k_w;
+    T* out = is_q ? src + (int64_t)h * D : dst_pool + (int64_t)(h - H) * D;
+    float v[C][4];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      const int d = (c * 32 + lane) * 4;
+      v[c][0] = v[c][1] = v[c][2] = v[c][3] = 0.f;
+      if (d < D) row_load4(in + d, v[c]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ss = fmaf(v[c][e], v[c][e], ss);
+    }
+    float rstd = 1.f;
+    if (w) rstd = 1.0f / sqrtf(warp_reduce_sum(ss) / (float)D + eps);
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      const int d = (c * 32 + lane) * 4;
+      if (d >= D) continue;
+      if (w) {
+        float g[4];
+        row_load4(w + d, g);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[c][e] = v[c][e] * rstd * g[e];
+      }
+#pragma unroll
+      for (int pr = 0; pr < 2; ++pr) {
+        const int dd = d + 2 * pr;
+        if (cs && dd < rot_dims) {
+          const float co = cs[dd >> 1], si = cs[half + (dd >> 1)];
+          const float a = v[c][2 * pr], b = v[c][2 * pr + 1];
+          v[c][2 * pr] = a * co - b * si;
+          v[c][2 * pr + 1] = b * co + a * si;
+        }
+      }
+      row_store4(out + d, v[c]);
+    }
+  }
+  const T* vin = src + (int64_t)(H + G) * D;
+  T* vout = dst_pool + (int64_t)G * D;
+  if ((G * Dv) % 4 == 0) {
+    for (int i = threadIdx.x * 4; i < G * Dv; i += blockDim.x * 4) {
+      float x[4];
+      row_load4(vin + i, x);
+      row_store4(vout + i, x);
+    }
+  } else {
+    for (int i = threadIdx.x; i < G * Dv; i += blockDim.x) vout[i] = vin[i];
+  }
+}
+
 }  // namespace
 
 extern "C" int b2l_rope_table_freqs(void* cos_sin_f32, const void* pos_i32, const void* freqs_f32, int64_t tokens,
@@ -106,12 +177,24 @@ extern "C" int b2l_head_norm_rope_prepare(void* qkv, int64_t qkv_row_stride, voi
   cudaStream_t st = (cudaStream_t)stream;
   const size_t smem = (size_t)kPrepWarps * head_dim * sizeof(float);
   B2L_REQUIRE(smem <= 48 * 1024, "head_norm_rope_prepare: head_dim %d too large", head_dim);
+#define B2L_PREP_VEC(CV)                                                                                            \
+  b2l_launch(head_norm_rope_prepare_vec_kernel<T, CV>, dim3((unsigned)tokens), dim3(kVecWarps * 32), (size_t)0, st, \
+             (T*)qkv, qkv_row_stride, (T*)kv_pool, kv_row_stride, (const int*)kv_rows_i32,                          \
+             (const float*)cos_sin_f32, (const T*)q_norm_weight, (const T*)k_norm_weight, heads, kv_heads, head_dim, \
+             v_head_dim, rot_dims, eps)
   B2L_DISPATCH_FLOAT(dtype, "head_norm_rope_prepare", {
+    const bool vec = pairing == 0 && head_dim % 4 == 0 && head_dim <= 256 && qkv_row_stride % 4 == 0 &&
+                     kv_row_stride % 4 == 0 && row_aligned4<T>(qkv) && row_aligned4<T>(kv_pool) &&
+                     row_aligned4<T>(q_norm_weight) && row_aligned4<T>(k_norm_weight) &&
+                     ((kv_heads * v_head_dim) % 4 != 0 || ((int64_t)(heads + kv_heads) * head_dim) % 4 == 0);
+    if (vec && head_dim <= 128) { B2L_PREP_VEC(1); B2L_LAUNCH_CHECK(); return B2L_OK; }
+    if (vec) { B2L_PREP_VEC(2); B2L_LAUNCH_CHECK(); return B2L_OK; }
     b2l_launch(head_norm_rope_prepare_kernel<T>, dim3((unsigned)tokens), dim3(kPrepWarps * 32), smem, st, (T*)qkv,
                qkv_row_stride, (T*)kv_pool, kv_row_stride, (const int*)kv_rows_i32, (const float*)cos_sin_f32,
                (const T*)q_norm_weight, (const T*)k_norm_weight, heads, kv_heads, head_dim, v_head_dim, rot_dims,
                pairing, eps);
   });
+#undef B2L_PREP_VEC
   B2L_LAUNCH_CHECK();
   return B2L_OK;
 }
