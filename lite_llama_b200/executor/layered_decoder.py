@@ -783,7 +783,7 @@ def map_tisosun_weights(cfg: LayeredConfig, tensors: dict[str, torch.Tensor], de
                       "down": get(f"l{i}.mlp.down")}
         if cfg.token_side_dim:
             lw.side = {"gate": get(f"l{i}.side.gate"), "proj": get(f"l{i}.side.proj"), "norm": get(f"l{i}.side.norm")}
-        if cfg.depth_average:
+        if cfg.depth_average and f"l{i}.dwa" in tensors:      # a layer without coefficients hands its result on as it is
             lw.depth = get(f"l{i}.dwa")
         out.layers.append(lw)
     return out

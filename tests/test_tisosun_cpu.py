@@ -32,8 +32,8 @@ def test_config_parser_reads_every_size_and_constant():
     assert isinstance(m, SideBySideSpec) and isinstance(m.left, BlockAttentionSpec)
     L = m.left
     assert (L.heads, L.kv_heads, L.head_dim, L.v_head_dim, L.block, L.softcap, L.rot_dims, L.rot_base) == \
-        (3, 1, 8, 10, 7, 20.0, 4, 10000.0)
-    assert (L.rot_factor, L.rot_original, L.rot_fast, L.rot_slow, L.pairing) == (4.0, 64.0, 32.0, 1.0, "neighbours")
+        (3, 1, 8, 10, 7, 15.0, 4, 10000.0)
+    assert (L.rot_factor, L.rot_original, L.rot_fast, L.rot_slow, L.pairing) == (3.0, 64.0, 16.0, 1.0, "neighbours")
     assert math.isclose(L.scale, 1 / math.sqrt(8)) and m.cache_row_width == 24 and m.state_shape == (2, 8, 6)
     assert m.right.decay == (0.6, 0.97)
     L2 = cfg.layers[3].mixer.left

@@ -103,7 +103,7 @@ def test_branches_join_the_residual_and_the_token_input(dtype, tol):
 def test_interpolated_frequencies_and_both_pairings():
     from lite_llama_b200.kernels import head_norm_rope_prepare, rope_table_freqs, rotary_frequencies
 
-    for dims, base, sc in ((48, 10000.0, {"factor": 4.0, "fast": 32.0, "original": 1024, "slow": 1.0}),
+    for dims, base, sc in ((40, 20000.0, {"factor": 6.0, "fast": 16.0, "original": 2048, "slow": 2.0}),
                            (8, 500.0, {"factor": 2.5, "fast": 4.0, "original": 64, "slow": 0.5}), (6, 100.0, None),
                            (64, 1e6, {"factor": 8.0, "fast": 1.0, "original": 4096, "slow": 1.0})):
         f, mag = rotary_frequencies(dims, base, **({"factor": sc["factor"], "original": sc["original"],
@@ -200,7 +200,7 @@ def test_minimal_gru_recurrence_over_portions_and_single_tokens(dtype, tol, widt
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 3e-2)])
-@pytest.mark.parametrize("width,blocks,taps", [(12, 3, 3), (64, 2, 4), (10, 1, 1), (6, 6, 2)])
+@pytest.mark.parametrize("width,blocks,taps", [(12, 3, 3), (64, 2, 4), (10, 1, 1), (6, 6, 2), (40, 5, 5)])
 def test_gated_lru_block_with_convolution_tail_and_block_gates(dtype, tol, width, blocks, taps):
     """The recurrence branch end to end (convolution with its tail, block-diagonal gates, recurrence, GELU branch)
     on a sequence cut into portions of 150, 2 and 1 tokens beside another sequence, against the restatement."""
@@ -311,7 +311,9 @@ def _attention_case(m, seqs, dtype, boost=None, seed=0):
                                   dict(heads=4, kv_heads=2, dim=64, vdim=64, rot_dims=64, chunk=128, softcap=0.0),
                                   dict(heads=2, kv_heads=2, dim=6, vdim=3, rot_dims=0, chunk=1, scaling=None),
                                   dict(heads=8, kv_heads=1, dim=16, vdim=24, rot_dims=8, chunk=200),
-                                  dict(heads=2, kv_heads=1, dim=16, vdim=8, rot_dims=6, chunk=0)])
+                                  dict(heads=2, kv_heads=1, dim=16, vdim=8, rot_dims=6, chunk=0),
+                                  dict(heads=2, kv_heads=1, dim=256, vdim=136, rot_dims=64, chunk=40),
+                                  dict(heads=6, kv_heads=3, dim=48, vdim=72, rot_dims=48, chunk=66)])
 def test_block_masked_attention_in_portions_and_single_tokens(dtype, tol, geom):
     """Portions that start and end inside a block, at its first and last position, span several blocks, and single
     tokens at the first, second and last position of a block, far into a sequence."""
@@ -328,7 +330,7 @@ def test_block_masked_attention_in_portions_and_single_tokens(dtype, tol, geom):
 def test_a_key_at_the_first_position_of_the_block_is_found_and_the_one_before_it_is_not(dtype, new):
     """One key among hundreds is made to stand out for the last query (a shared direction with a large gain, no soft
     cap): inside the query's block it takes the softmax, one position earlier it changes nothing."""
-    size = 96
+    size = 80
     m = O.attention_entry(heads=2, kv_heads=1, dim=16, vdim=8, rot_dims=0, chunk=size, softcap=0.0, scaling=None,
                           scale=2.0)                                      # aligned q.k = 32 against +-8 by chance
     cached = 3 * size + 50 - new                                          # the last query sits at position 3*size + 49
@@ -344,7 +346,7 @@ def test_a_key_at_the_first_position_of_the_block_is_found_and_the_one_before_it
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 3e-2)])
-@pytest.mark.parametrize("heads,dim,vdim", [(2, 8, 6), (4, 64, 32), (1, 5, 1), (3, 24, 40)])
+@pytest.mark.parametrize("heads,dim,vdim", [(2, 8, 6), (4, 64, 32), (1, 5, 1), (3, 24, 40), (2, 80, 72), (1, 200, 16)])
 def test_decayed_linear_attention_memory_over_portions_and_single_tokens(dtype, tol, heads, dim, vdim):
     from lite_llama_b200.kernels import linear, norm_sigmoid_gate, ssm_scan
 
@@ -385,7 +387,7 @@ def _aligned():
     # sizes in steps of 8: the tensor-core tiles in bf16; one block longer than a 64-key tile, one of exactly two tiles
     a = O.attention_entry(heads=6, kv_heads=1, dim=32, vdim=24, rot_dims=16, chunk=70)
     b = O.attention_entry(heads=4, kv_heads=2, dim=64, vdim=64, rot_dims=64, chunk=128, softcap=0.0)
-    return O.make_config([O.parallel_layer(a, O.decay_entry(4, 32, 16, (0.6, 0.88, 0.97, 0.999)), ff=64),
+    return O.make_config([O.parallel_layer(a, O.decay_entry(4, 32, 16, (0.7, 0.9, 0.98, 0.995)), ff=64),
                           O.mingru_layer(width=72, ff=64), O.rglru_layer(width=64, blocks=4, conv=4, ff=32),
                           O.parallel_layer(b, O.decay_entry(2, 64, 32, (0.95, 0.5)), ff=64)], width=64, vocab=128, side_dim=8)
 
@@ -441,6 +443,24 @@ def test_whole_prompt_portions_and_decoding_agree_with_the_restatement(name, len
         runner.close_request(req)
     assert runner.kv_cache_manager.can_use_mem_size == runner.kv_cache_manager.max_num_tokens
     assert runner.state_manager.free_slots == 4
+
+
+@pytest.mark.parametrize("layers", ["recurrent_only", "attention_only"])
+def test_models_without_a_cache_or_with_nothing_else(layers):
+    """A model whose layers keep no rows in the pool (the pool has no layer to serve), and one of parallel layers only;
+    the first runs past the pool's size since it holds no rows that matter."""
+    if layers == "recurrent_only":
+        cfg = O.make_config([O.mingru_layer(), O.rglru_layer(ff=None), O.mingru_layer(width=6)], side_dim=2)
+    else:
+        cfg = O.make_config([O.parallel_layer(ff=None), O.parallel_layer(O.attention_entry(chunk=0, scaling=None))])
+    w = O.random_model(cfg, seed=15)
+    toks = _tokens(cfg, 50, 4)
+    ref = O.forward(cfg, w, toks)
+    runner = _runner(cfg, w, max_tokens=64)
+    req = runner.open_request()
+    _close(_feed(runner, req, toks, [20, 2]), ref, 1e-4)
+    runner.close_request(req)
+    assert runner.kv_cache_manager.can_use_mem_size == 64
 
 
 def test_layer_results_match_one_by_one():
@@ -616,7 +636,7 @@ def _random_config(rng, odd):
                                 "original": rng.choice([16, 64, 1024]), "slow": rng.choice([0.5, 1.0])}])
         return O.attention_entry(heads=kv * rng.choice([1, 2, 6]), kv_heads=kv, dim=dim,
                                  vdim=rng.choice([3, 10, 33] if odd else [8, 24, 80]), rot_dims=rot,
-                                 base=rng.choice([100.0, 10000.0, 1.0e6]), chunk=rng.choice([1, 2, 5, 16, 33, 64, 65, 96, 128, 200, 1000]),
+                                 base=rng.choice([100.0, 10000.0, 1.0e6]), chunk=rng.choice([1, 2, 5, 16, 33, 64, 65, 100, 128, 200, 1000]),
                                  softcap=rng.choice([0.0, 5.0, 30.0]), scaling=sc if rot else None)
 
     def right():

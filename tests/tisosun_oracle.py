@@ -242,10 +242,10 @@ def forward(config: dict, tensors: dict, tokens: list[int], return_layers: bool 
 
 
 # ------------------------------------------------------------------------------------- configurations for tests #
-def attention_entry(heads=3, kv_heads=1, dim=8, vdim=10, rot_dims=4, base=10000.0, chunk=7, softcap=20.0,
+def attention_entry(heads=3, kv_heads=1, dim=8, vdim=10, rot_dims=4, base=10000.0, chunk=7, softcap=15.0,
                     scaling="default", scale=None) -> dict:
     if scaling == "default":
-        scaling = {"factor": 4.0, "fast": 32.0, "original": 64, "slow": 1.0}
+        scaling = {"factor": 3.0, "fast": 16.0, "original": 64, "slow": 1.0}
     rot = {"base": base, "dims": rot_dims}
     if scaling:
         rot["scaling"] = scaling
