@@ -31,6 +31,21 @@ __device__ __forceinline__ float gelu_tanh_gr(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// Gate arithmetic in two grades: true fp32 library functions when the activations are fp32 (the exact mode), and
+// ex2.approx-based forms (relative error ~2^-22, far below the rounding of the 16-bit projections that feed the gates)
+// when they are 16-bit: the library forms cost ~200 dependent instructions per token and channel, which bound the
+// kernel at the occupancy its registers allow.
+constexpr float kLog2eG = 1.4426950408889634f;
+template <bool FAST> __device__ __forceinline__ float sigm(float v) {
+  return FAST ? __fdividef(1.0f, 1.0f + fast_exp2(-v * kLog2eG)) : sigmoid_f(v);
+}
+template <bool FAST> __device__ __forceinline__ float gelu_t(float z) {
+  if (!FAST) return gelu_tanh_gr(z);
+  const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  const float th = 1.0f - __fdividef(2.0f, fast_exp2(u * (2.0f * kLog2eG)) + 1.0f);
+  return 0.5f * z * (1.0f + th);
+}
+
 struct ScanArgs {
   const void* p[4];
   int64_t ps[4];
@@ -43,12 +58,13 @@ struct ScanArgs {
 };
 
 template <typename T, int MODE>
-__global__ void __launch_bounds__(kWarps * 32) gated_scan_kernel(ScanArgs k) {
+__global__ void __launch_bounds__(kWarps * 32, 2) gated_scan_kernel(ScanArgs k) {
   pdl_prologue();
   __shared__ float sA[kWarps][32], sB[kWarps][32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + lane;
   const bool live = c < k.width;
+  constexpr bool FAST = sizeof(T) == 2;
   const int s = blockIdx.y;
   const int start = k.seq_start[s], len = k.seq_start[s + 1] - start, ctx = k.seq_ctx[s];
   if (len <= 0) return;
@@ -86,17 +102,22 @@ __global__ void __launch_bounds__(kWarps * 32) gated_scan_kernel(ScanArgs k) {
     for (int j = 0; j < kSeg; ++j) {
       if (j < cnt && live) {
         if (MODE == 0) {
-          const float z = sigmoid_f(v0[j]);
-          const float cand = v1[j] >= 0.f ? v1[j] + 0.5f : sigmoid_f(v1[j]);
+          const float z = sigm<FAST>(v0[j]);
+          const float cand = v1[j] >= 0.f ? v1[j] + 0.5f : sigm<FAST>(v1[j]);
           a[j] = 1.0f - z;
           b[j] = z * cand;
-          g[j] = v2[j] * sigmoid_f(v2[j]);
+          g[j] = v2[j] * sigm<FAST>(v2[j]);
         } else {
-          const float r = sigmoid_f(v1[j] + br), i = sigmoid_f(v2[j] + bi);
+          const float r = sigm<FAST>(v1[j] + br), i = sigm<FAST>(v2[j] + bi);
           const float la = rate * r;                       // log a <= 0
-          a[j] = expf(la);
-          b[j] = sqrtf(fmaxf(-expm1f(2.0f * la), 0.f)) * i * v0[j];      // sqrt(1 - a^2) without cancellation
-          g[j] = gelu_tanh_gr(v3[j]);
+          if (FAST) {
+            a[j] = fast_exp2(la * kLog2eG);
+            b[j] = sqrtf(fmaxf(1.0f - a[j] * a[j], 0.f)) * i * v0[j];
+          } else {
+            a[j] = expf(la);
+            b[j] = sqrtf(fmaxf(-expm1f(2.0f * la), 0.f)) * i * v0[j];    // sqrt(1 - a^2) without cancellation
+          }
+          g[j] = gelu_t<FAST>(v3[j]);
         }
         B = fmaf(a[j], B, b[j]);
         A *= a[j];
