@@ -396,13 +396,6 @@ int b2l_branch_sum_residual(void* residual_f32, void* act, const void* a, int64_
 int b2l_gelu_mul_gather(void* out, const void* z, int64_t z_row_stride, const void* tokens_i32, const void* table,
                         int64_t table_row_stride, int64_t vocab, int col0, int dim, int64_t rows, int dtype,
                         void* stream);
-/* The whole token input of a small step in one launch (one CTA per token): z = gate . x, g = gelu_tanh(z) * table row,
- * y = proj . g, residual += unit_rms(y) * norm_weight; gate [dim, n], proj [n, dim].  Rows of up to
- * b2l_token_side_input_max_width(dim) elements. */
-int64_t b2l_token_side_input_max_width(int dim);
-int b2l_token_side_input(void* residual_f32, const void* gate, const void* proj, const void* norm_weight,
-                         const void* tokens_i32, const void* table, int64_t table_row_stride, int64_t vocab, int col0,
-                         int dim, int64_t rows, int64_t n, float eps, int dtype, void* stream);
 
 /* Element-wise gated recurrences S_t = a_t S_(t-1) + b_t, o_t = S_t g_t over a ragged step (csrc/gated_recurrence.cu).
  * mode 0 (minimal GRU): p0 / p1 / p2 = update-gate, candidate, output-gate pre-activations.  mode 1 (real-gated LRU):

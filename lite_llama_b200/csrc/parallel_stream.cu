@@ -8,10 +8,6 @@
 //                           b and c optional): a mixer with one or two normed branches plus a feed-forward output
 //                           joining the residual in one pass; optional copy of the new x in T for the next GEMM
 //   * gelu_mul_gather       o[t, d] = gelu_tanh(z[t, d]) * table[token[t], col0 + d]       (per-layer token input)
-//   * token_side_input      the whole token input of a SMALL step in one launch, one CTA per token:
-//                           z = W_gate x;  g = gelu_tanh(z) * table row;  y = W_proj g;  x += unit_rms(y) * w
-//                           (x, z, g and y are rounded to T where the separate kernels round them: products in T with
-//                           fp32 sums, the norm and the residual sum in fp32)
 // unit_rms(v) = v / sqrt(mean(v^2) + eps).  All statistics, sums and the stack itself are fp32.
 #include "common.cuh"
 #include "rowvec.cuh"
@@ -261,91 +257,7 @@ __global__ void gelu_mul_gather_kernel(T* __restrict__ o, const T* __restrict__ 
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(256) token_side_input_kernel(float* __restrict__ r, const T* __restrict__ gate,
-                                                               const T* __restrict__ proj, const T* __restrict__ w,
-                                                               const int* __restrict__ tokens,
-                                                               const T* __restrict__ table, int64_t table_stride,
-                                                               int64_t vocab, int col0, int dim, int64_t n, float eps,
-                                                               int vec) {
-  pdl_prologue();
-  extern __shared__ __align__(16) float side_sm[];
-  __shared__ float red[32];
-  float* xs = side_sm;                 // [n] the residual row as the gate product reads it (rounded to T)
-  float* ys = xs + n;                  // [n] the projected row (rounded to T)
-  float* gs = ys + n;                  // [dim]
-  const int64_t t = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  float* rr = r + t * n;
-  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) xs[i] = to_f32(from_f32<T>(rr[i]));
-  int64_t tok = tokens[t];
-  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
-  __syncthreads();
-  for (int d = warp; d < dim; d += nw) {                       // one warp per gate row
-    const T* g = gate + (int64_t)d * n;
-    float acc = 0.f;
-    if (vec) {
-      for (int64_t i = (int64_t)lane * 4; i < n; i += 128) {
-        float q[4];
-        row_load4(g + i, q);
-        acc = fmaf(q[0], xs[i], fmaf(q[1], xs[i + 1], fmaf(q[2], xs[i + 2], fmaf(q[3], xs[i + 3], acc))));
-      }
-    } else {
-      for (int64_t i = lane; i < n; i += 32) acc = fmaf(to_f32(g[i]), xs[i], acc);
-    }
-    acc = warp_reduce_sum(acc);
-    if (lane == 0) {
-      const float z = to_f32(from_f32<T>(acc));
-      gs[d] = to_f32(from_f32<T>(gelu_tanh_f(z) * to_f32(table[tok * table_stride + col0 + d])));
-    }
-  }
-  __syncthreads();
-  float ss = 0.f;
-  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {      // one thread per projection row
-    const T* p = proj + i * dim;
-    float acc = 0.f;
-    if (vec) {
-      for (int d = 0; d < dim; d += 4) {
-        float q[4];
-        row_load4(p + d, q);
-        acc = fmaf(q[0], gs[d], fmaf(q[1], gs[d + 1], fmaf(q[2], gs[d + 2], fmaf(q[3], gs[d + 3], acc))));
-      }
-    } else {
-      for (int d = 0; d < dim; ++d) acc = fmaf(to_f32(p[d]), gs[d], acc);
-    }
-    const float y = to_f32(from_f32<T>(acc));
-    ys[i] = y;
-    ss = fmaf(y, y, ss);
-  }
-  const float rstd = 1.0f / sqrtf(block_sum_ps(ss, red) / (float)n + eps);
-  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) rr[i] += ys[i] * rstd * to_f32(w[i]);
-}
-
 }  // namespace
-
-extern "C" int64_t b2l_token_side_input_max_width(int dim) {
-  const int64_t room = 48 * 1024 / 4 - dim;         // floats of shared memory: two rows and the gate vector
-  return room > 0 ? room / 2 : 0;
-}
-
-extern "C" int b2l_token_side_input(void* residual_f32, const void* gate, const void* proj, const void* norm_weight,
-                                    const void* tokens_i32, const void* table, int64_t table_row_stride, int64_t vocab,
-                                    int col0, int dim, int64_t rows, int64_t n, float eps, int dtype, void* stream) {
-  B2L_REQUIRE(residual_f32 && gate && proj && norm_weight && tokens_i32 && table, "token_side_input: null pointer");
-  B2L_REQUIRE(rows >= 0 && n > 0 && dim > 0 && col0 >= 0 && col0 + dim <= table_row_stride, "token_side_input: bad shape");
-  B2L_REQUIRE(n <= b2l_token_side_input_max_width(dim), "token_side_input: rows of %lld elements do not fit", (long long)n);
-  if (rows == 0) return B2L_OK;
-  cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem = (size_t)(2 * n + dim) * sizeof(float);
-  B2L_DISPATCH_FLOAT(dtype, "token_side_input", {
-    const int vec = n % 4 == 0 && dim % 4 == 0 && row_aligned4<T>(gate) && row_aligned4<T>(proj);
-    b2l_launch(token_side_input_kernel<T>, dim3((unsigned)rows), dim3(256), smem, st, (float*)residual_f32, (const T*)gate,
-               (const T*)proj, (const T*)norm_weight, (const int*)tokens_i32, (const T*)table, table_row_stride, vocab,
-               col0, dim, n, eps, vec);
-  });
-  B2L_LAUNCH_CHECK();
-  return B2L_OK;
-}
 
 extern "C" int b2l_embed_rmsnorm(void* residual_f32, const void* tokens_i32, const void* embed, const void* weight,
                                  int64_t rows, int64_t n, int64_t vocab, float eps, float weight_offset, float scale,

@@ -66,8 +66,6 @@ from ..kernels import (
     softcap_to_f32,
     ssm_scan,
     swiglu_forward,
-    token_side_fits,
-    token_side_input,
 )
 from .model_config import (BlockAttentionSpec, DecayAttentionSpec, DenseMlpSpec, LatentAttentionSpec, LayeredConfig,
                            LayerSpec, Mamba2Spec, MinGruSpec, MoeMlpSpec, RgLruSpec, SideBySideSpec, SinkAttentionSpec)
@@ -425,13 +423,9 @@ class LayeredDecoder:
             y = MIXERS[spec.kind](li, spec.mixer, lw.mix, h1, ctx, eps)
             f = FEED_FORWARDS[spec.mlp.kind](spec.mlp, lw.mlp, h2) if spec.mlp is not None else None
             br = y if isinstance(y, Branches) else Branches(y, None)
-            fused_side = lw.side is not None and token_side_fits(T, n, cfg.token_side_dim)
             act = branch_sum_residual(x, br.a, br.a_weight, br.b, br.b_weight, f, eps, br.scale,
-                                      want_act=lw.side is not None and not fused_side)
-            if fused_side:                               # small steps: the whole token input is one launch
-                token_side_input(x, tokens, lw.side["gate"], lw.side["proj"], lw.side["norm"], w.side_embed,
-                                 li * cfg.token_side_dim, eps)
-            elif lw.side is not None:
+                                      want_act=lw.side is not None)
+            if lw.side is not None:
                 d = cfg.token_side_dim
                 z = linear(x if act is None else act, lw.side["gate"])
                 g = gelu_mul_gather(z, tokens, w.side_embed, li * d)

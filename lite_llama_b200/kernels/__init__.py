@@ -10,8 +10,7 @@ from .flashdecoding import flash_decoding
 from .fused_moe import fused_moe, grouped_experts, moe_align_block_size, route_sigmoid_groups, route_topk
 from .latent import head_linear, latent_prepare, rope_heads, rope_table
 from .linear import linear, linear_simt
-from .parallel_stream import (branch_sum_residual, depth_mix_norms, embed_rmsnorm, gelu_mul_gather, token_side_fits,
-                              token_side_input)
+from .parallel_stream import branch_sum_residual, depth_mix_norms, embed_rmsnorm, gelu_mul_gather
 from .rotary_heads import head_norm_rope_prepare, rope_table_freqs, rotary_frequencies
 from .residual_stream import embed_positions, gelu, post_norm_residual, relu_squared, rmsnorm_from_f32, softcap_to_f32
 from .sink_attention import attn_prepare, sink_attention
@@ -55,8 +54,6 @@ __all__ = [
     "depth_mix_norms",
     "branch_sum_residual",
     "gelu_mul_gather",
-    "token_side_input",
-    "token_side_fits",
     "rope_table_freqs",
     "rotary_frequencies",
     "head_norm_rope_prepare",

@@ -97,29 +97,3 @@ def gelu_mul_gather(z: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, 
                                     table.stride(0), table.shape[0], int(col0), dim, rows, float_code(z, "z"),
                                     stream_handle()))
     return out
-
-
-TOKEN_SIDE_FUSED_ROWS = 64          # steps of up to this many tokens take the one-launch token input
-
-
-def token_side_fits(rows: int, n: int, dim: int) -> bool:
-    """Whether ``token_side_input`` serves a step of ``rows`` tokens of width ``n``."""
-    return rows <= TOKEN_SIDE_FUSED_ROWS and n <= lib().b2l_token_side_input_max_width(int(dim))
-
-
-@torch.no_grad()
-def token_side_input(residual: torch.Tensor, tokens: torch.Tensor, gate: torch.Tensor, proj: torch.Tensor,
-                     norm_weight: torch.Tensor, table: torch.Tensor, col0: int, eps: float) -> None:
-    """``residual += unit_rms(proj @ (gelu_tanh(gate @ x) * table[tokens, col0:col0 + dim])) * norm_weight`` per token
-    in ONE launch (small steps; the products read and round their operands as the separate kernels do)."""
-    require_cuda(residual, tokens, gate, proj, norm_weight, table)
-    rows, n = residual.shape
-    dim = gate.shape[0]
-    if residual.dtype != torch.float32 or not residual.is_contiguous() or tokens.dtype != torch.int32:
-        raise ValueError("token_side_input: fp32 contiguous residual, int32 tokens")
-    if gate.shape != (dim, n) or proj.shape != (n, dim) or not gate.is_contiguous() or not proj.is_contiguous() or \
-            gate.dtype != proj.dtype or table.dtype != gate.dtype or norm_weight.dtype != gate.dtype or table.stride(-1) != 1:
-        raise ValueError("token_side_input: bad layout")
-    check(lib().b2l_token_side_input(residual.data_ptr(), gate.data_ptr(), proj.data_ptr(), norm_weight.data_ptr(),
-                                     tokens.data_ptr(), table.data_ptr(), table.stride(0), table.shape[0], int(col0), dim,
-                                     rows, n, float(eps), float_code(gate, "gate"), stream_handle()))

@@ -100,31 +100,6 @@ def test_branches_join_the_residual_and_the_token_input(dtype, tol):
     _close(got, O.gelu_tanh(O.f64(z)) * O.f64(table)[toks][:, 14:21], tol)
 
 
-@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("n,dim", [(52, 7), (256, 16), (1100, 64)])
-def test_token_input_in_one_launch_equals_its_four_steps(dtype, tol, n, dim):
-    from lite_llama_b200.kernels import gelu_mul_gather, linear, post_norm_residual, token_side_fits, token_side_input
-
-    T, eps, vocab, layers = 5, 1e-5, 23, 3
-    assert token_side_fits(T, n, dim) and not token_side_fits(65, n, dim) and not token_side_fits(T, 7000, dim)
-    r0 = torch.randn(T, n)
-    gate, proj = (torch.randn(dim, n) / math.sqrt(n)).to(dtype), (torch.randn(n, dim) / math.sqrt(dim)).to(dtype)
-    nw, table = (0.5 + 0.1 * torch.randn(n)).to(dtype), torch.randn(vocab, layers * dim).to(dtype)
-    toks = [22, 0, 7, 7, 13]
-    r = r0.to(DEV)
-    token_side_input(r, _i32(toks), gate.to(DEV), proj.to(DEV), nw.to(DEV), table.to(DEV), 2 * dim, eps)
-    x = O.f64(r0.to(dtype)) if dtype != torch.float32 else O.f64(r0)
-    ref = O.f64(r0) + np.stack([O.norm_plain(O.f64(proj) @ (O.gelu_tanh(O.f64(gate) @ x[t]) * O.f64(table)[toks[t], 2 * dim:3 * dim]),
-                                             O.f64(nw), eps) for t in range(T)])
-    _close(r, ref, tol)
-    # the separate kernels give the same up to the order of the sums
-    r2 = r0.to(DEV)
-    act = r2.to(dtype)
-    g = gelu_mul_gather(linear(act, gate.to(DEV)), _i32(toks), table.to(DEV), 2 * dim)
-    post_norm_residual(r2, linear(g, proj.to(DEV)), nw.to(DEV), eps, 0.0, want_act=False)
-    _close(r, r2.double().cpu(), 1e-5 if dtype == torch.float32 else 1e-2)
-
-
 def test_interpolated_frequencies_and_both_pairings():
     from lite_llama_b200.kernels import head_norm_rope_prepare, rope_table_freqs, rotary_frequencies
 
@@ -486,6 +461,25 @@ def test_models_without_a_cache_or_with_nothing_else(layers):
     _close(_feed(runner, req, toks, [20, 2]), ref, 1e-4)
     runner.close_request(req)
     assert runner.kv_cache_manager.can_use_mem_size == 64
+
+
+@pytest.mark.parametrize("stacked", [True, False])
+def test_without_depth_coefficients_every_layer_reads_the_previous_result(stacked):
+    """A checkpoint without the depth coefficients: the layers follow one another; with the depth average switched off
+    in the configuration two levels alternate instead of a stack."""
+    from lite_llama_b200.executor import ModelRunner
+    from lite_llama_b200.executor.registry import lookup
+
+    cfg = CONFIGS["small"]()
+    w = {k: v for k, v in O.random_model(cfg, seed=19).items() if not k.endswith(".dwa")}
+    toks = _tokens(cfg, 30, 9)
+    ref = O.forward(cfg, w, toks)
+    arch = lookup("Tisosun")
+    conf = arch.parse_config(cfg)
+    if not stacked:
+        conf = conf.with_(depth_average=False)
+    runner = ModelRunner(conf, arch.map_weights(conf, w, DEV, torch.float32), 64, device=DEV, dtype=torch.float32)
+    _close(_feed(runner, runner.open_request(), toks, [17, 2]), ref, 1e-4)
 
 
 def test_layer_results_match_one_by_one():
