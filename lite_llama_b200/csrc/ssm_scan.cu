@@ -506,12 +506,17 @@ extern "C" int b2l_ssm_scan(void* y_f32, void* state_f32, const void* xbc, int64
   if (num_seqs <= 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
   // two columns per lane when the head is wider than a warp and the state rows still fit 12 compute warps
-  const int cpl = (head_dim > 32 && state_size <= 384) ? 2 : 1;
+  // (a state of up to 64 rows fits one warp's registers at one column per lane: no slices, no partial sums)
+  const int cpl = (head_dim > 32 && state_size > 64 && state_size <= 384) ? 2 : 1;
   const int npt = state_size <= 16 ? 16 : ((state_size <= 32 || cpl == 2) ? 32 : 64);
   const int nslices = (state_size + npt - 1) / npt;
   int ctiles = (head_dim + 32 * cpl - 1) / (32 * cpl);
   const int room = 8 / nslices > 1 ? 8 / nslices : 1;      // compute warps <= 12 with the 4 loaders: <= 512 threads
   if (ctiles > room) ctiles = room;
+  // the token loop of a CTA is serial, so the grid is all the parallelism there is: with sliced states (several
+  // compute warps per column tile) narrower column tiles until two CTAs per SM are there to be had; B and C are then
+  // staged once per tile, which the loader warps absorb.  (Unsliced states lose: one compute warp per four loaders.)
+  while (cpl == 2 && ctiles > 1 && cdiv64(head_dim, (int64_t)ctiles * 32 * cpl) * heads * num_seqs < 2 * 148) --ctiles;
   const int cols = ctiles * 32 * cpl, np = nslices * npt;
   const size_t smem = (size_t)(2 * (2 * kChunk * np + kChunk * cols + 2 * kChunk) +
                                (nslices > 1 ? 2 * nslices * kChunk * cols : 0)) * sizeof(float);
