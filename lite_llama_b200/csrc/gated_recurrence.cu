@@ -10,7 +10,8 @@
 //
 // p0 .. p3 are column views of projection outputs in T (row strides given); gates, decays and the state are fp32.
 // The recurrence is associative, so a CTA = (32 channels, sequence) cuts its tokens into segments of kSeg: each of
-// its kWarps warps loads one segment (kSeg independent loads per input in flight), reduces it to the pair
+// its kWarps warps loads one segment (kSeg independent loads per input in flight; 16 warps of 8 tokens at no more
+// than 64 registers, so that two CTAs share an SM: occupancy, not arithmetic, bounds the kernel), reduces it to the pair
 // (A = prod a, B = its end state from zero), the pairs are chained through shared memory from the CTA's running
 // state, and each warp then replays its segment from registers with the right start value.  A single new token takes
 // the same path with one live warp.  A sequence with seq_ctx == 0 starts from zero: slots need no clearing.
@@ -22,8 +23,8 @@
 
 namespace {
 
-constexpr int kSeg = 16;
-constexpr int kWarps = 8;
+constexpr int kSeg = 8;
+constexpr int kWarps = 16;
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ float softplus_gr(float v) { return v > 20.f ? v : log1pf(expf(v)); }
