@@ -678,7 +678,7 @@ def tisosun_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) 
     rows_p = tab[:, :ctx].reshape(-1).contiguous()
     rot = D // 2
     f, mag = K.rotary_frequencies(rot, 10000.0, 4.0, 4096.0, 32.0, 1.0)
-    freqs = torch.tensor(f, dtype=torch.float32, device=dev)
+    freqs = torch.tensor(f, dtype=torch.float64, device=dev)
     cs = K.rope_table_freqs(pos_p, freqs, mag)
     add("rope_table_freqs (once per step)", "rope_table", lambda: K.rope_table_freqs(pos_p, freqs, mag),
         nbytes=T * (4 + rot * 4), like_fn=lambda: K.rope_table(pos_p, rot, 10000.0))

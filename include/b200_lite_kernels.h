@@ -411,10 +411,10 @@ int b2l_norm_sigmoid_gate(void* out, const void* y_f32, const void* z, int64_t z
                           int64_t rows, int n, float eps, int dtype, void* stream);
 
 /* Rotary table from given per-pair frequencies (csrc/rotary_heads.cu): cos_sin_f32[t] = magnitude * [cos(pos f_i) |
- * sin(pos f_i)], fp32 angles.  head_norm_rope_prepare: per token of a fused [q | k | v] row, per-head RMS norm of q and
+ * sin(pos f_i)], fp64 frequencies and angles.  head_norm_rope_prepare: per token of a fused [q | k | v] row, per-head RMS norm of q and
  * k with one [head_dim] weight each (nullable), rotation of the first rot_dims entries (pairing 0: neighbours 2i, 2i+1;
  * 1: i and i + rot_dims / 2), q in place, k and v into pool row kv_rows[t]. */
-int b2l_rope_table_freqs(void* cos_sin_f32, const void* pos_i32, const void* freqs_f32, int64_t tokens, int rot_dims,
+int b2l_rope_table_freqs(void* cos_sin_f32, const void* pos_i32, const void* freqs_f64, int64_t tokens, int rot_dims,
                          float magnitude, void* stream);
 int b2l_head_norm_rope_prepare(void* qkv, int64_t qkv_row_stride, void* kv_pool, int64_t kv_row_stride,
                                const void* kv_rows_i32, const void* cos_sin_f32, const void* q_norm_weight,

@@ -1,29 +1,30 @@
 // Rotary positions with per-pair frequencies given as a table (frequency-interpolated variants compute the table on
 // the host), and the per-token preparation of attention layers that norm each head on its own:
 //   * rope_table_freqs         cos_sin[t] = [mag * cos(pos[t] * f_i), i < rot_dims / 2 | mag * sin(pos[t] * f_i)],
-//                              the angle is the fp32 product of the position and the fp32 frequency
+//                              frequencies and angles in fp64 (an fp32 angle of a thousand radians is already off by
+//                              6e-5), the table in fp32; once per step
 //   * head_norm_rope_prepare   per token of a fused [q | k | v] projection row: every q head and every k head is
 //                              RMS-normed over its own head_dim entries with ONE weight [head_dim] shared by the heads
 //                              (nullable = no norm), then its first rot_dims entries are rotated (pairing 0: entries
 //                              2i and 2i+1; pairing 1: entries i and i + rot_dims / 2); q is updated in place, k and v
 //                              go to pool row kv_rows[t] = [k heads | v heads].
-// Statistics, angles and the rotation are fp32; one rounding to T at the end.
+// Statistics and the rotation are fp32; one rounding to T at the end.
 #include "common.cuh"
 #include "rowvec.cuh"
 
 namespace {
 
 __global__ void rope_table_freqs_kernel(float* __restrict__ out, const int* __restrict__ pos,
-                                        const float* __restrict__ freqs, int64_t total, int half, float mag) {
+                                        const double* __restrict__ freqs, int64_t total, int half, float mag) {
   pdl_prologue();
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = idx / half;
     const int i = (int)(idx - t * half);
-    const float a = (float)pos[t] * freqs[i];
-    float sn, cs;
-    sincosf(a, &sn, &cs);
-    out[t * 2 * half + i] = cs * mag;
-    out[t * 2 * half + half + i] = sn * mag;
+    const double a = (double)pos[t] * freqs[i];
+    double sn, cs;
+    sincos(a, &sn, &cs);
+    out[t * 2 * half + i] = (float)(cs * (double)mag);
+    out[t * 2 * half + half + i] = (float)(sn * (double)mag);
   }
 }
 
@@ -149,16 +150,16 @@ __global__ void __launch_bounds__(kVecWarps * 32) head_norm_rope_prepare_vec_ker
 
 }  // namespace
 
-extern "C" int b2l_rope_table_freqs(void* cos_sin_f32, const void* pos_i32, const void* freqs_f32, int64_t tokens,
+extern "C" int b2l_rope_table_freqs(void* cos_sin_f32, const void* pos_i32, const void* freqs_f64, int64_t tokens,
                                     int rot_dims, float magnitude, void* stream) {
-  B2L_REQUIRE(cos_sin_f32 && pos_i32 && freqs_f32, "rope_table_freqs: null pointer");
+  B2L_REQUIRE(cos_sin_f32 && pos_i32 && freqs_f64, "rope_table_freqs: null pointer");
   B2L_REQUIRE(rot_dims > 0 && rot_dims % 2 == 0, "rope_table_freqs: %d rotated entries", rot_dims);
   if (tokens <= 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t total = tokens * (rot_dims / 2);
   const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
   b2l_launch(rope_table_freqs_kernel, dim3(grid), dim3(256), (size_t)0, st, (float*)cos_sin_f32, (const int*)pos_i32,
-             (const float*)freqs_f32, total, rot_dims / 2, magnitude);
+             (const double*)freqs_f64, total, rot_dims / 2, magnitude);
   B2L_LAUNCH_CHECK();
   return B2L_OK;
 }

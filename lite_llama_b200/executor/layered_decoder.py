@@ -736,7 +736,7 @@ def map_tisosun_weights(cfg: LayeredConfig, tensors: dict[str, torch.Tensor], de
     """Checkpoint names -> the decoder's weights.  Every mixer's input projections are row-concatenated into one GEMM
     weight with one bias vector (zeros where a projection has none); the attention half is padded with zero rows to a
     multiple of 8 so that the linear-attention half starts on a 16-byte boundary, and its columns are ordered
-    [values | keys | queries | gate], the layout the scan kernel reads.  Decays and rotary frequencies are fp32."""
+    [values | keys | queries | gate], the layout the scan kernel reads.  Decays are fp32, rotary frequencies fp64."""
 
     def get(name: str) -> torch.Tensor:
         if name not in tensors:
@@ -767,8 +767,7 @@ def map_tisosun_weights(cfg: LayeredConfig, tensors: dict[str, torch.Tensor], de
             rq = torch.cat([get(p + "right.v"), get(p + "right.k"), get(p + "right.q"), get(p + "right.g")], dim=0)
             key = (L.rot_dims, L.rot_base, L.rot_factor, L.rot_original, L.rot_fast, L.rot_slow)
             if L.rot_dims and key not in freq_cache:
-                freq_cache[key] = torch.tensor(rotary_frequencies(*key)[0], dtype=torch.float64).to(
-                    device=device, dtype=torch.float32)
+                freq_cache[key] = torch.tensor(rotary_frequencies(*key)[0], dtype=torch.float64).to(device=device)
             mix = {"in": torch.cat([lq, rq], dim=0).contiguous(), "in_b": torch.cat([lb, zeros(rq.shape[0])]),
                    "q_norm": get(p + "left.q.norm"), "k_norm": get(p + "left.k.norm"), "left_o": get(p + "left.o"),
                    "right_norm": get(p + "right.norm"), "right_o": get(p + "right.o"), "left_out": get(p + "left.out"),

@@ -40,10 +40,11 @@ def rotary_frequencies(dims: int, base: float, factor: float = 1.0, original: fl
 
 @torch.no_grad()
 def rope_table_freqs(positions: torch.Tensor, freqs: torch.Tensor, magnitude: float = 1.0) -> torch.Tensor:
-    """fp32 ``[T, 2 * len(freqs)]`` = per token ``magnitude * [cos | sin]`` of ``position * freqs[i]`` (fp32 angle)."""
+    """fp32 ``[T, 2 * len(freqs)]`` = per token ``magnitude * [cos | sin]`` of ``position * freqs[i]``; the frequencies
+    are an fp64 tensor and the angles are formed and evaluated in fp64."""
     require_cuda(positions, freqs)
-    if freqs.dtype != torch.float32 or positions.dtype != torch.int32:
-        raise ValueError("rope_table_freqs: int32 positions, fp32 frequencies")
+    if freqs.dtype != torch.float64 or positions.dtype != torch.int32 or not freqs.is_contiguous():
+        raise ValueError("rope_table_freqs: int32 positions, fp64 frequencies")
     dims = 2 * freqs.numel()
     out = torch.empty((positions.numel(), dims), dtype=torch.float32, device=positions.device)
     check(lib().b2l_rope_table_freqs(out.data_ptr(), positions.data_ptr(), freqs.data_ptr(), positions.numel(), dims,

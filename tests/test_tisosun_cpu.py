@@ -90,7 +90,7 @@ def test_weight_mapping_fuses_the_input_projections():
     assert torch.equal(mix["in"][76:92], w["l0.mix.right.q"]) and torch.equal(mix["in"][92:], w["l0.mix.right.g"])
     assert mix["decay"].dtype == torch.float32 and mix["decay"].tolist() == [np.float32(0.6), np.float32(0.97)]
     ref_f, _ = O.yarn_frequencies(4, 10000.0, raw["layers"][0]["mixer"]["left"]["rot"]["scaling"])
-    assert mix["freqs"].dtype == torch.float32 and np.allclose(mix["freqs"].numpy(), ref_f, rtol=1e-6)
+    assert mix["freqs"].dtype == torch.float64 and np.allclose(mix["freqs"].numpy(), ref_f, rtol=1e-14)
     r = wt.layers[1].mix
     assert r["in"].shape == (24, 20) and torch.equal(r["in"][12:], w["l1.mix.x"]) and torch.equal(r["in_b"][:12], w["l1.mix.y.b"])
     assert r["ra"].shape == (3, 4, 4) and r["ra_b"].shape == (12,) and torch.equal(r["ri_b"][4:8], w["l1.mix.ri.b"][1])
