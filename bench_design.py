@@ -545,7 +545,7 @@ def tisosun_config(sz: dict) -> dict:
            "mixer": {"left": {"dim": sz["head_dim"], "heads": sz["heads"], "kv_heads": sz["kv_heads"],
                               "mask": {"size": sz["chunk"]},
                               "rot": {"base": 10000.0, "dims": sz["head_dim"] // 2,
-                                      "scaling": {"factor": 4.0, "fast": 32.0, "original": 4096, "slow": 1.0}},
+                                      "scaling": {"factor": 8.0, "fast": 32.0, "original": 4096, "slow": 1.0}},
                               "scale": 1.0 / math.sqrt(sz["head_dim"]), "softcap": 30.0, "vdim": sz["head_dim"]},
                      "right": {"decay": [1.0 - 2.0 ** (-2 - 6 * h / sz["r_heads"]) for h in range(sz["r_heads"])],
                                "dim": sz["r_dim"], "heads": sz["r_heads"], "vdim": sz["r_vdim"]}}}
@@ -677,7 +677,7 @@ def tisosun_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) 
     qkv = rnd(T, (H + 2 * G) * D, s=0.5)
     rows_p = tab[:, :ctx].reshape(-1).contiguous()
     rot = D // 2
-    f, mag = K.rotary_frequencies(rot, 10000.0, 4.0, 4096.0, 32.0, 1.0)
+    f, mag = K.rotary_frequencies(rot, 10000.0, 8.0, 4096.0, 32.0, 1.0)
     freqs = torch.tensor(f, dtype=torch.float64, device=dev)
     cs = K.rope_table_freqs(pos_p, freqs, mag)
     add("rope_table_freqs (once per step)", "rope_table", lambda: K.rope_table_freqs(pos_p, freqs, mag),
