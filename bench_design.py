@@ -722,8 +722,13 @@ def tisosun_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) 
     dtb, alog, dsk = rnd(SH), rnd(SH, s=0.5), rnd(SH)
     sst = torch.zeros(batch, SH, SN, SP, device=dev)
     xr = rproj[:, :rin + 2 * RH * RD]
-    add("ssm_scan, fixed decay (prompts)", "ssm_scan (state-space, prompts)",
+    add("ssm_scan, fixed decay (prompts; the fp32 and odd-size path)", "ssm_scan (state-space, prompts)",
         lambda: K.ssm_scan(xr, None, None, None, None, rst, p_start, p_ctx, p_slot, RH, RH, RD, RV, fixed_decay=dec, silu_inputs=True),
+        nbytes=T * ((rin + 2 * RH * RD) * es + rin * 4) + batch * RH * RD * RV * 4,
+        like_fn=lambda: K.ssm_scan(xbc, sproj, dtb, alog, dsk, sst, p_start, p_ctx, p_slot, SH, SG, SN, SP),
+        like_bytes=T * ((inner + 2 * gn) * es + SH * es + inner * 4) + batch * SH * SP * SN * 4)
+    add("decay_attention (prompts, 64-token chunks on the tensor cores)", "ssm_scan (state-space, prompts)",
+        lambda: K.decay_attention(xr, rst, dec, p_start, p_ctx, p_slot, RH, RD, RV, prompt),
         nbytes=T * ((rin + 2 * RH * RD) * es + rin * 4) + batch * RH * RD * RV * 4,
         like_fn=lambda: K.ssm_scan(xbc, sproj, dtb, alog, dsk, sst, p_start, p_ctx, p_slot, SH, SG, SN, SP),
         like_bytes=T * ((inner + 2 * gn) * es + SH * es + inner * 4) + batch * SH * SP * SN * 4)

@@ -351,6 +351,13 @@ int b2l_ssm_scan(void* y_f32, void* state_f32, const void* xbc, int64_t xbc_row_
                  const void* seq_start, const void* seq_ctx, const void* seq_slot, int64_t num_seqs, int heads,
                  int groups, int state_size, int head_dim, const void* fixed_decay_f32, int silu_inputs, int dtype,
                  void* stream);
+/* The fixed-decay case of b2l_ssm_scan with SiLU inputs, over prompt portions in chunks of 64 tokens on the tensor
+ * cores (csrc/decay_attention_mma.cu): same y_f32 and state_f32; x rows = [v: heads*head_dim | k: heads*state_size |
+ * q: heads*state_size].  b2l_decay_attention_mma_ok: 16-bit dtype, both sizes in {32, 64, 128}, 16-byte aligned rows. */
+int b2l_decay_attention_mma_ok(const void* x, int64_t x_row_stride, int state_size, int head_dim, int dtype);
+int b2l_decay_attention_mma(void* y_f32, void* state_f32, const void* x, int64_t x_row_stride, const void* decay_f32,
+                            const void* seq_start, const void* seq_ctx, const void* seq_slot, int64_t num_seqs, int heads,
+                            int state_size, int head_dim, int dtype, void* stream);
 /* out = unit_rms(y * silu(z)) * weight, the unit RMS taken in `groups` equal parts of the row. */
 int b2l_gated_group_norm(void* out, const void* y_f32, const void* z, int64_t z_row_stride, const void* weight,
                          int64_t rows, int inner, int groups, float eps, int dtype, void* stream);

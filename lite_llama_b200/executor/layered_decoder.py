@@ -41,6 +41,7 @@ from ..kernels import (
     attn_prepare,
     branch_sum_residual,
     causal_conv_silu,
+    decay_attention,
     depth_mix_norms,
     embed_positions,
     embed_rmsnorm,
@@ -276,8 +277,9 @@ def side_by_side_mixer(li: int, spec: SideBySideSpec, w: dict[str, torch.Tensor]
                        eps: float) -> Branches:
     """ONE projection for both halves, [q | k | v (biased) | pad || v' | k' | q' | gate'].  Left: per-head norms,
     rotation and the cache write in one kernel, attention over the pool under the block-diagonal mask, out-projection.
-    Right: the fixed-decay scan against the slot's fp32 memory (SiLU applied as the scan reads its inputs), row norm
-    and sigmoid gate, out-projection.  The two outputs go to the residual kernel as branches."""
+    Right: decayed linear attention against the slot's fp32 memory (SiLU applied as the kernel reads its inputs; chunks
+    on the tensor cores for prompt portions, the token-by-token scan otherwise), row norm and sigmoid gate,
+    out-projection.  The two outputs go to the residual kernel as branches."""
     b, L, R = ctx.batch, spec.left, spec.right
     proj = linear(x, w["in"], w["in_b"])
     # ---- left: softmax attention over the pool
@@ -300,8 +302,8 @@ def side_by_side_mixer(li: int, spec: SideBySideSpec, w: dict[str, torch.Tensor]
     r0 = -(-(L.heads * L.head_dim + L.kv_heads * (L.head_dim + L.v_head_dim)) // 8) * 8     # padded attention half
     inner = R.heads * R.v_head_dim
     xbc = proj[:, r0:r0 + inner + 2 * R.heads * R.head_dim]
-    y = ssm_scan(xbc, None, None, None, None, ctx.states.ssm_state[li], b.seq_start, b.seq_ctx, b.seq_slot, R.heads,
-                 R.heads, R.head_dim, R.v_head_dim, fixed_decay=w["decay"], silu_inputs=True)
+    y = decay_attention(xbc, ctx.states.ssm_state[li], w["decay"], b.seq_start, b.seq_ctx, b.seq_slot, R.heads,
+                        R.head_dim, R.v_head_dim, max(b.max_portion, 1))
     gate = proj[:, r0 + inner + 2 * R.heads * R.head_dim:r0 + 2 * inner + 2 * R.heads * R.head_dim]
     right = linear(norm_sigmoid_gate(y, gate, w["right_norm"], eps), w["right_o"])
     return Branches(left, w["left_out"], right, w["right_out"], 0.5)
@@ -856,6 +858,6 @@ def random_tisosun_tensors(cfg: LayeredConfig, seed: int = 0) -> dict[str, torch
 
 
 _TISOSUN_SOURCES = ("gemm_dense", "gemm_simt", "gemm_rows_mma", "residual_stream", "parallel_stream", "gated_recurrence",
-                    "rotary_heads", "ssm_scan", "attention_sink", "elementwise")
+                    "rotary_heads", "ssm_scan", "decay_attention_mma", "attention_sink", "elementwise")
 register(Architecture("Tisosun", parse_tisosun_config, map_tisosun_weights, LayeredDecoder, ragged_steps=True,
                       sources=_TISOSUN_SOURCES))

@@ -14,7 +14,7 @@ from .parallel_stream import branch_sum_residual, depth_mix_norms, embed_rmsnorm
 from .rotary_heads import head_norm_rope_prepare, rope_table_freqs, rotary_frequencies
 from .residual_stream import embed_positions, gelu, post_norm_residual, relu_squared, rmsnorm_from_f32, softcap_to_f32
 from .sink_attention import attn_prepare, sink_attention
-from .ssm import causal_conv_silu, gated_group_norm, gated_scan, norm_sigmoid_gate, ssm_scan
+from .ssm import causal_conv_silu, decay_attention, gated_group_norm, gated_scan, norm_sigmoid_gate, ssm_scan
 from .rope_emb import rope_emb_forward, rope_emb_inplace, rope_kv_write
 from .sampling import argmax_rows
 from .skip_rmsnorm import can_fuse_int8_quant, skip_rmsnorm, skip_rmsnorm_quant_int8
@@ -49,6 +49,7 @@ __all__ = [
     "ssm_scan",
     "gated_group_norm",
     "gated_scan",
+    "decay_attention",
     "norm_sigmoid_gate",
     "embed_rmsnorm",
     "depth_mix_norms",

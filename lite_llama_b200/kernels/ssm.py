@@ -61,6 +61,33 @@ def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, gro
     return out
 
 
+DECAY_ATTENTION_CHUNK = 64
+
+
+@torch.no_grad()
+def decay_attention(x: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, seq_start, seq_ctx, seq_slot, heads: int,
+                    state_size: int, head_dim: int, longest: int) -> torch.Tensor:
+    """Decayed linear attention ``S <- decay_h S + k v^T``, ``y = S^T q`` on SiLU'd ``x = [v | k | q]`` columns (a view
+    of the fused projection): ``y [tokens, heads*head_dim]`` fp32, ``state [slots, heads, state_size, head_dim]`` fp32
+    advanced in place.  Steps whose longest sequence brings at least half a chunk of tokens run chunk by chunk on the
+    tensor cores when the geometry allows (16-bit activations, sizes of 32 / 64 / 128); everything else -- single
+    tokens, fp32, other sizes -- runs the token-by-token scan (``ssm_scan`` with fixed decays)."""
+    require_cuda(x, state, decay)
+    if state.dtype != torch.float32 or decay.dtype != torch.float32 or decay.numel() != heads:
+        raise ValueError("decay_attention: fp32 state, fp32 decays [heads]")
+    L = lib()
+    code = float_code(x, "x")
+    if longest >= DECAY_ATTENTION_CHUNK // 2 and x.stride(-1) == 1 and \
+            L.b2l_decay_attention_mma_ok(x.data_ptr(), x.stride(0), state_size, head_dim, code):
+        y = torch.empty((x.shape[0], heads * head_dim), dtype=torch.float32, device=x.device)
+        check(L.b2l_decay_attention_mma(y.data_ptr(), state.data_ptr(), x.data_ptr(), x.stride(0), decay.data_ptr(),
+                                        seq_start.data_ptr(), seq_ctx.data_ptr(), seq_slot.data_ptr(), seq_ctx.numel(),
+                                        heads, state_size, head_dim, code, stream_handle()))
+        return y
+    return ssm_scan(x, None, None, None, None, state, seq_start, seq_ctx, seq_slot, heads, heads, state_size, head_dim,
+                    fixed_decay=decay, silu_inputs=True)
+
+
 @torch.no_grad()
 def norm_sigmoid_gate(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """``unit_rms(y) * weight * sigmoid(z)`` over whole rows: the gate acts AFTER the norm (``gated_group_norm`` gates

@@ -373,6 +373,44 @@ def test_decayed_linear_attention_memory_over_portions_and_single_tokens(dtype, 
     assert (state[0] == 4.0).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("heads,dim,vdim", [(4, 64, 32), (2, 128, 128), (1, 32, 64), (3, 64, 64), (2, 32, 32), (1, 32, 128),
+                                            (2, 64, 128), (3, 128, 32), (1, 128, 64)])
+def test_linear_attention_in_chunks_on_the_tensor_cores_and_token_by_token_share_one_memory(dtype, heads, dim, vdim):
+    """Two sequences side by side: portions of 150, 70 and 33 tokens (chunks of 64 with ragged ends, on the tensor
+    cores), of 2 tokens and single tokens (the scan) advance the same fp32 memories; a fast and a very slow decay."""
+    from lite_llama_b200.kernels import decay_attention, norm_sigmoid_gate
+
+    decay = [0.5, 0.999, 1.0, 0.9][:heads]
+    m = O.decay_entry(heads=heads, dim=dim, vdim=vdim, decay=decay)
+    inner, kq = heads * vdim, heads * dim
+    cols = inner + 2 * kq + inner
+    g = torch.Generator().manual_seed(dim + vdim)
+    xs = [torch.randn(n, cols, generator=g).to(dtype) for n in (300, 120)]
+    nw = (1 + 0.2 * torch.randn(inner, generator=g)).to(dtype)
+    w = {"v": _select(range(0, inner), cols), "k": _select(range(inner, inner + kq), cols),
+         "q": _select(range(inner + kq, inner + 2 * kq), cols), "g": _select(range(inner + 2 * kq, cols), cols),
+         "norm": O.f64(nw), "o": np.eye(inner)}
+    refs = [O.decay_attention(O.f64(x), m, w, 1e-5) for x in xs]
+    state = torch.full((3, heads, dim, vdim), 4.0, device=DEV)
+    dec = torch.tensor(decay, dtype=torch.float32, device=DEV)
+    plan = [[(0, 0, 150), (1, 0, 33)], [(1, 33, 35), (0, 150, 220)], [(0, 220, 221)], [(0, 221, 254), (1, 35, 36)],
+            [(1, 36, 120), (0, 254, 256)], [(0, 256, 300)]]
+    got = {0: [], 1: []}
+    for step in plan:
+        part = torch.cat([xs[i][a:b] for i, a, b in step]).to(DEV)
+        meta = _ragged([(b - a, a, i + 1) for i, a, b in step])
+        y = decay_attention(part[:, :inner + 2 * kq], state, dec, *meta, heads, dim, vdim, max(b - a for _, a, b in step))
+        out = norm_sigmoid_gate(y, part[:, inner + 2 * kq:], nw.to(DEV), 1e-5)
+        at = 0
+        for i, a, b in step:
+            got[i].append(out[at:at + b - a])
+            at += b - a
+    for i in (0, 1):
+        _close(torch.cat(got[i]), refs[i], 2e-2)
+    assert (state[0] == 4.0).all()
+
+
 # ------------------------------------------------------------------------------------------------- whole models #
 def _small():
     # nothing a multiple of 8, three query heads on one kv head, blocks shorter than a portion
