@@ -67,49 +67,71 @@ __global__ void __launch_bounds__(kDaWarps * 32) decay_attention_mma_kernel(DaAr
   const int inner = H * Pf;
   const int64_t voff = (int64_t)h * Pf + p0, koff = (int64_t)inner + (int64_t)h * N, qoff = (int64_t)inner + (int64_t)H * N + (int64_t)h * N;
   bool carried = ctx > 0;                                      // the memory is non-zero
-  for (int c0 = 0; c0 < len; c0 += kC) {
+  // A chunk's rows travel global -> registers -> (SiLU, scaling, halves) -> shared memory; the loads of the NEXT chunk
+  // are issued before the products of the current one and land while they run.
+  constexpr int QV = kC * (N / 8) / (kDaWarps * 32), VV = kC * (P / 8) / (kDaWarps * 32);
+  uint4 pq[QV], pk[QV], pv[VV];
+  auto fetch = [&](int c0) {
     const int cnt = min(kC, len - c0);
-    __syncthreads();                                           // dpw / sS ready; the previous chunk's tiles are free
-    // ---- stage the chunk: SiLU in fp32, one rounding to T; rows past the end are zero
-    for (int i = tid; i < kC * (N / 8); i += blockDim.x) {
-      const int j = i / (N / 8), c = (i - j * (N / 8)) * 8;
-      uint4 rq = make_uint4(0u, 0u, 0u, 0u), rk = rq;
+#pragma unroll
+    for (int u = 0; u < QV; ++u) {
+      const int i = tid + u * (kDaWarps * 32), j = i / (N / 8), c = (i - j * (N / 8)) * 8;
+      pq[u] = pk[u] = make_uint4(0u, 0u, 0u, 0u);
       if (j < cnt) {
         const T* row = x + (int64_t)(start + c0 + j) * a.x_stride;
-        const uint4 gq4 = ldg_128(row + qoff + c), gk4 = ldg_128(row + koff + c);
-        const T* eq = reinterpret_cast<const T*>(&gq4);
-        const T* ek = reinterpret_cast<const T*>(&gk4);
-        T* oq = reinterpret_cast<T*>(&rq);
-        T* ok = reinterpret_cast<T*>(&rk);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) { oq[u] = from_f32<T>(silu_da(to_f32(eq[u]))); ok[u] = from_f32<T>(silu_da(to_f32(ek[u]))); }
+        pq[u] = ldg_128(row + qoff + c);
+        pk[u] = ldg_128(row + koff + c);
       }
+    }
+#pragma unroll
+    for (int u = 0; u < VV; ++u) {
+      const int i = tid + u * (kDaWarps * 32), j = i / (P / 8), c = (i - j * (P / 8)) * 8;
+      pv[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (j < cnt) pv[u] = ldg_128(x + (int64_t)(start + c0 + j) * a.x_stride + voff + c);
+    }
+  };
+  // SiLU in fp32, one rounding to T; rows past the end are zero (SiLU(0) = 0)
+  auto commit = [&](int cnt) {
+#pragma unroll
+    for (int u = 0; u < QV; ++u) {
+      const int i = tid + u * (kDaWarps * 32), j = i / (N / 8), c = (i - j * (N / 8)) * 8;
+      uint4 rq, rk;
+      const T* eq = reinterpret_cast<const T*>(&pq[u]);
+      const T* ek = reinterpret_cast<const T*>(&pk[u]);
+      T* oq = reinterpret_cast<T*>(&rq);
+      T* ok = reinterpret_cast<T*>(&rk);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { oq[e] = from_f32<T>(silu_da(to_f32(eq[e]))); ok[e] = from_f32<T>(silu_da(to_f32(ek[e]))); }
       *reinterpret_cast<uint4*>(sQ + j * QP + c * 2) = rq;
       *reinterpret_cast<uint4*>(sK + j * QP + c * 2) = rk;
     }
-    for (int i = tid; i < kC * (P / 8); i += blockDim.x) {
-      const int j = i / (P / 8), c = (i - j * (P / 8)) * 8;
-      uint4 rv = make_uint4(0u, 0u, 0u, 0u), rh = rv, rl = rv;
-      if (j < cnt) {
-        const uint4 gv4 = ldg_128(x + (int64_t)(start + c0 + j) * a.x_stride + voff + c);
-        const T* ev = reinterpret_cast<const T*>(&gv4);
-        T* ov = reinterpret_cast<T*>(&rv);
-        T* oh = reinterpret_cast<T*>(&rh);
-        T* ol = reinterpret_cast<T*>(&rl);
-        const float w = dpw[cnt - 1 - j];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const float v = silu_da(to_f32(ev[u]));
-          ov[u] = from_f32<T>(v);
-          const float sv = to_f32(ov[u]) * w;                  // the rounded value is THE v of this path
-          oh[u] = from_f32<T>(sv);
-          ol[u] = from_f32<T>(sv - to_f32(oh[u]));
-        }
+    for (int u = 0; u < VV; ++u) {
+      const int i = tid + u * (kDaWarps * 32), j = i / (P / 8), c = (i - j * (P / 8)) * 8;
+      uint4 rv, rh, rl;
+      const T* ev = reinterpret_cast<const T*>(&pv[u]);
+      T* ov = reinterpret_cast<T*>(&rv);
+      T* oh = reinterpret_cast<T*>(&rh);
+      T* ol = reinterpret_cast<T*>(&rl);
+      const float w = j < cnt ? dpw[cnt - 1 - j] : 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        ov[e] = from_f32<T>(silu_da(to_f32(ev[e])));
+        const float sv = to_f32(ov[e]) * w;                    // the rounded value is THE v of this path
+        oh[e] = from_f32<T>(sv);
+        ol[e] = from_f32<T>(sv - to_f32(oh[e]));
       }
       *reinterpret_cast<uint4*>(sV + j * VP + c * 2) = rv;
       *reinterpret_cast<uint4*>(sVh + j * VP + c * 2) = rh;
       *reinterpret_cast<uint4*>(sVl + j * VP + c * 2) = rl;
     }
+  };
+  fetch(0);
+  for (int c0 = 0; c0 < len; c0 += kC) {
+    const int cnt = min(kC, len - c0);
+    __syncthreads();                                           // dpw / sS ready; the previous chunk's tiles are free
+    commit(cnt);
+    if (c0 + kC < len) fetch(c0 + kC);
     __syncthreads();
     // ---- outputs of the warp's 16 tokens
     const int r0 = warp * 16 + gq, r1 = r0 + 8;                 // rows of the chunk
