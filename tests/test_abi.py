@@ -22,7 +22,7 @@ def test_header_parses_and_declares_the_hot_path_ops():
     for name, (ret, args) in protos.items():
         if ret == "int" and name not in ("b2l_version", "b2l_device_info", "b2l_set_pdl", "b2l_hang_report", "b2l_tp_comm_handle_bytes",
                                           "b2l_tp_comm_get_handle", "b2l_tp_comm_open", "b2l_tp_comm_destroy",
-                                          "b2l_moe_gemm_simt_block", "b2l_rows_gemm_mma_ok"):          # pure queries
+                                          "b2l_moe_gemm_simt_block", "b2l_rows_gemm_mma_ok", "b2l_decay_attention_mma_ok"):          # pure queries
             assert args[-1] == "void*", f"{name} must end with the stream argument"
 
 
