@@ -30,11 +30,11 @@ for step in $STEPS; do
         python bench.py --steps 2 --warmup 1 --no-cpu-baseline --no-breakdown > gpurun_out/launches_bench.log 2>&1
       echo "launches exit=$?" >> $S ;;
     ncu_gemm)
-      timeout 240 ncu --set full --clock-control none --import-source on -k regex:gemm_quant_kernel -s 2 -c 1 -f -o gpurun_out/w4a16_gateup \
+      timeout 240 ncu --set full --clock-control none -k regex:gemm_quant_kernel -s 2 -c 1 -f -o gpurun_out/w4a16_gateup \
         python tools/prof_kernels.py --op w4a16 --m 32 --n 28672 --k 4096 > gpurun_out/ncu_gemm.log 2>&1
       echo "ncu_gemm exit=$?" >> $S ;;
     ncu_decode)
-      timeout 240 ncu --set full --clock-control none --import-source on -k regex:flash_decode_split -s 2 -c 1 -f -o gpurun_out/flash_decoding_ctx8192 \
+      timeout 240 ncu --set full --clock-control none -k regex:flash_decode_split -s 2 -c 1 -f -o gpurun_out/flash_decoding_ctx8192 \
         python tools/prof_kernels.py --op decode --ctx 8192 > gpurun_out/ncu_decode.log 2>&1
       echo "ncu_decode exit=$?" >> $S ;;
     timeline)

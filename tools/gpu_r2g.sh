@@ -10,7 +10,7 @@ run bench 200 python bench.py --steps 64 --warmup 4 --no-cpu-baseline
 run bench_noswiglu 200 env B2L_FUSE_SWIGLU=0 python bench.py --steps 64 --warmup 4 --no-cpu-baseline
 run bench_moe 300 python bench.py --model qwen3-30b-a3b --quant fp8 --steps 32 --warmup 4 --no-cpu-baseline --watchdog-s 280
 run triton_moe 200 python tools/bench_triton_ref.py --only fused_moe --out gpurun_out/r2g_triton_moe
-NCU="ncu --set full --clock-control none --import-source on -f"
+NCU="ncu --set full --clock-control none -f"
 run launches 300 ncu --metrics gpu__time_duration.sum --clock-control none --csv --log-file gpurun_out/launches.csv python bench.py --steps 2 --warmup 1 --no-cpu-baseline --no-breakdown
 run ncu_gateup 200 $NCU -k regex:gemm_quant_kernel -s 2 -c 1 -o gpurun_out/r2g_w4a16_gateup python tools/prof_kernels.py --op w4a16 --m 32 --n 28672 --k 4096
 run ncu_o 200 $NCU -k regex:gemm_quant_kernel -s 2 -c 1 -o gpurun_out/r2g_w4a16_o python tools/prof_kernels.py --op w4a16 --m 32 --n 4096 --k 4096

@@ -11,7 +11,7 @@ run triton_fa 200 python tools/bench_triton_ref.py --only flash_attention --out 
 run triton_moe 200 python tools/bench_triton_ref.py --only fused_moe --out gpurun_out/r2g2_triton_moe
 run bench_moe 300 python bench.py --model qwen3-30b-a3b --quant fp8 --steps 32 --warmup 4 --no-cpu-baseline --watchdog-s 280
 run launches 400 ncu --metrics gpu__time_duration.sum --clock-control none --csv --log-file gpurun_out/launches.csv python bench.py --layers 8 --steps 2 --warmup 3 --no-cpu-baseline --no-breakdown
-run ncu_fa2048 200 ncu --set full --clock-control none --import-source on -f -k regex:fa_tc_kernel -s 2 -c 1 -o gpurun_out/r2g2_fa_tc_v2_s2048 python tools/prof_kernels.py --op prefill --m 4 --ctx 2048
+run ncu_fa2048 200 ncu --set full --clock-control none -f -k regex:fa_tc_kernel -s 2 -c 1 -o gpurun_out/r2g2_fa_tc_v2_s2048 python tools/prof_kernels.py --op prefill --m 4 --ctx 2048
 cat $S
 echo "== fa_tests"; tail -12 gpurun_out/r2g2_fa_tests.out
 echo "== tests"; tail -12 gpurun_out/r2g2_tests.out
