@@ -281,8 +281,8 @@ int b2l_rmsnorm_from_f32(void* out, const void* residual_f32, const void* rows_i
 int b2l_relu_squared(void* out, const void* x, int64_t total, int dtype, void* stream);
 /* out = gelu(x): exact (erf) form, or the tanh form 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))). */
 int b2l_gelu(void* out, const void* x, int64_t total, int tanh_form, int dtype, void* stream);
-/* out_f32 = cap * tanh(x / cap) (cap <= 0: x) as fp32: soft-capped logits. */
-int b2l_softcap_to_f32(void* out_f32, const void* x, int64_t total, float cap, int dtype, void* stream);
+/* out_f32 = cap * tanh(scale * x / cap) (cap <= 0: scale * x) as fp32: scaled, soft-capped logits. */
+int b2l_softcap_to_f32(void* out_f32, const void* x, int64_t total, float cap, float scale, int dtype, void* stream);
 /* y[t, h, :] = W[h] . x[t, h, :] for W [heads, n, k] (csrc/gemm_simt.cu); x / y rows hold the heads side by side
  * (strides in elements); gate (nullable) [m, >= heads]: y[t, h, :] *= sigmoid(gate[t, h]). */
 int b2l_head_linear(void* y, int64_t y_row_stride, int64_t y_head_stride, const void* x, int64_t x_row_stride,
@@ -312,10 +312,12 @@ int b2l_moe_gemm_mma(void* c, const void* a, const void* w, const void* slot_wei
  * unless logits_f32 [tokens, experts] (nullable) brings it:
  * z = router_w . x in fp32, s = sigmoid(z), choice = s + bias (nullable); `groups` equal runs of neighbouring experts,
  * group score = sum of its two largest choice scores, only the `keep` best groups are eligible; the top_k largest
- * choice scores win; weights_f32 [tokens, top_k] = s of the winners / (their sum + 1e-20); ids_i32 [tokens, top_k]. */
+ * choice scores win; weights_f32 [tokens, top_k] = s of the winners / (their sum + 1e-20), or with renormalize 0 the
+ * winners' s themselves; ids_i32 [tokens, top_k]. */
 int b2l_moe_route_sigmoid_groups(void* weights_f32, void* ids_i32, const void* x, int64_t x_row_stride,
                                  const void* router_w, const void* bias, const void* logits_f32, int64_t tokens,
-                                 int num_experts, int64_t k, int top_k, int groups, int keep, int dtype, void* stream);
+                                 int num_experts, int64_t k, int top_k, int groups, int keep, int renormalize,
+                                 int dtype, void* stream);
 /* y_f32[m, n] = x[m, k] . w[n, k]^T: 16-bit operands on the tensor cores, the fp32 sums stored unrounded (router
  * logits); operands as b2l_rows_gemm_mma_ok asks. */
 int b2l_linear_f32out_mma(void* y_f32, const void* x, const void* w, int64_t m, int64_t n, int64_t k,
@@ -381,15 +383,17 @@ int b2l_sink_attention(void* out, int64_t out_row_stride, const void* q, int64_t
                        int64_t kv_row_stride, const void* table_i32, int64_t table_row_stride, const void* seq_start,
                        const void* seq_ctx, const void* seq_slot, const void* seq_list, int64_t num_seqs,
                        int max_q_len, const void* sink, int heads, int kv_heads, int head_dim, int v_head_dim,
-                       float scale, float softcap, int window, int block, int v_col0, int num_splits, int split_keys,
-                       void* workspace, int64_t workspace_bytes, int dtype, void* stream);
+                       float scale, float softcap, int window, int block, int v_col0, int v_head_stride,
+                       int num_splits, int split_keys, void* workspace, int64_t workspace_bytes, int dtype,
+                       void* stream);
 
 /* Parallel-block layer-list models with a depth-weighted residual stack (csrc/parallel_stream.cu).
  * embed_rmsnorm: residual_f32[t] = unit_rms(scale * embed[token[t]]) * (weight_offset + weight) (weight nullable).
  * depth_mix_norms: x = sum_j coef[j] * stack[j] over `count` levels `level_stride` floats apart (coef NULL: x = the last
  * level), written to x_out_f32 (nullable when n % 4 == 0 and n <= 8192), h1 = unit_rms(x) * (offset + w1), h2 likewise
- * (both nullable).  branch_sum_residual: residual += scale * (a' + b') + c with a' = unit_rms(a) * a_weight when the
- * weight is given, else a (b likewise; b, c nullable); act (nullable) = the new residual in dtype.
+ * (both nullable).  branch_sum_residual: residual += scale * a' + scale_b * b' + c with a' = unit_rms(a) * a_weight when
+ * the weight is given, else a (b likewise; b, c nullable); act (nullable) = the new residual in dtype, or, with
+ * next_weight, unit_rms(new residual) * next_weight (the input norm of the block that follows).
  * gelu_mul_gather: out[t, d] = gelu_tanh(z[t, d]) * table[token[t], col0 + d], d < dim. */
 int b2l_embed_rmsnorm(void* residual_f32, const void* tokens_i32, const void* embed, const void* weight, int64_t rows,
                       int64_t n, int64_t vocab, float eps, float weight_offset, float scale, int dtype, void* stream);
@@ -398,8 +402,8 @@ int b2l_depth_mix_norms(void* x_out_f32, void* h1, void* h2, const void* stack_f
                         float weight_offset, int dtype, void* stream);
 int b2l_branch_sum_residual(void* residual_f32, void* act, const void* a, int64_t a_row_stride, const void* a_weight,
                             const void* b, int64_t b_row_stride, const void* b_weight, const void* c,
-                            int64_t c_row_stride, int64_t rows, int64_t n, float eps, float scale, int dtype,
-                            void* stream);
+                            int64_t c_row_stride, const void* next_weight, int64_t rows, int64_t n, float eps,
+                            float scale, float scale_b, int dtype, void* stream);
 int b2l_gelu_mul_gather(void* out, const void* z, int64_t z_row_stride, const void* tokens_i32, const void* table,
                         int64_t table_row_stride, int64_t vocab, int col0, int dim, int64_t rows, int dtype,
                         void* stream);
@@ -416,6 +420,32 @@ int b2l_gated_scan(void* out, int64_t out_row_stride, void* state_f32, const voi
 /* out = unit_rms(y_f32) * weight * sigmoid(z) over whole rows of n. */
 int b2l_norm_sigmoid_gate(void* out, const void* y_f32, const void* z, int64_t z_row_stride, const void* weight,
                           int64_t rows, int n, float eps, int dtype, void* stream);
+
+/* Linear attention with data-dependent gates over a ragged step (csrc/gated_linear_attention.cu); state_f32 [slots,
+ * heads, dim, vdim] is advanced in place, y_f32 [tokens, heads * vdim].
+ * mode 0, forget-gate form: q [tokens, heads*dim] pre-activation (SiLU inside), k = forget-gate logits [tokens,
+ * heads*dim], c0 = lower bounds [heads*dim]: f = c0 + (1 - c0) sigmoid(k); S[d,:] <- f[d] S[d,:] + (1 - f[d]) v; o = S^T q.
+ * mode 1, gated delta rule: q, k [tokens, qk_heads*dim] (made unit vectors with unit_eps inside the root; q times
+ * q_scale), p0 / p1 = write-strength and decay logits [tokens, heads], c0 = dt_bias, c1 = A_log [heads]:
+ * g = exp(-exp(c1) softplus(p1 + c0)), S <- g S, u = sigmoid(p0) (v - S^T k), S <- S + k u^T, o = S^T q. */
+int b2l_gated_linear_scan(void* y_f32, void* state_f32, const void* q, int64_t q_row_stride, const void* k,
+                          int64_t k_row_stride, const void* v, int64_t v_row_stride, const void* p0,
+                          int64_t p0_row_stride, const void* p1, int64_t p1_row_stride, const void* c0, const void* c1,
+                          const void* seq_start, const void* seq_ctx, const void* seq_slot, int64_t num_seqs, int heads,
+                          int qk_heads, int dim, int vdim, float q_scale, float unit_eps, int mode, int dtype,
+                          void* stream);
+/* out[t, h, :] = unit_rms(y_f32[t, h, :]) * weight[vdim] * silu(gate[t, h, :]) (gate nullable: no gate). */
+int b2l_head_norm_gate(void* out, const void* y_f32, const void* gate, int64_t gate_row_stride, const void* weight,
+                       int64_t rows, int heads, int vdim, float eps, int dtype, void* stream);
+/* out[t, h, :] = sum_g mix[h, g] * wide[t, g, kv(h), :] for wide [rows, calls, heads, per_call, vdim] (kv head c of
+ * query head g lies at call c / per_call, part c % per_call): softmax weights mixed across heads, on the outputs. */
+int b2l_head_mix(void* out, const void* wide, int64_t wide_row_stride, const void* mix, int64_t rows, int heads,
+                 int kv_heads, int per_call, int vdim, int dtype, void* stream);
+/* out[r, :] = silu(s_r * gate[r, :]) * (s_r * up[r, :]) * sigmoid(z[r]); in_scale_f32 [rows] and z (one value per row,
+ * row stride given) are nullable. */
+int b2l_swiglu_scaled(void* out, int64_t out_row_stride, const void* gate, int64_t gate_row_stride, const void* up,
+                      int64_t up_row_stride, const void* in_scale_f32, const void* z, int64_t z_row_stride, int64_t rows,
+                      int64_t n, int dtype, void* stream);
 
 /* Rotary table from given per-pair frequencies (csrc/rotary_heads.cu): cos_sin_f32[t] = magnitude * [cos(pos f_i) |
  * sin(pos f_i)], fp64 frequencies and angles.  head_norm_rope_prepare: per token of a fused [q | k | v] row, per-head RMS norm of q and

@@ -70,7 +70,7 @@ BASE_SOURCES = ("core", "tma_desc")
 # latent-attention kernels, expert routing, argmax and expert sum.  Each
 # registered architecture names its own subset (executor.registry.Architecture.sources).
 LAYERED_SOURCES = ("gemm_dense", "gemm_simt", "gemm_rows_mma", "residual_stream", "parallel_stream", "ssm_scan",
-                   "decay_attention_mma", "gated_recurrence", "attention_sink", "rotary_heads", "latent_attention", "moe_routing", "elementwise")
+                   "decay_attention_mma", "gated_recurrence", "gated_linear_attention", "attention_sink", "rotary_heads", "latent_attention", "moe_routing", "elementwise")
 LINK_STAMP = OBJ_DIR / "link.stamp"
 
 

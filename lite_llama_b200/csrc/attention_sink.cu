@@ -40,6 +40,8 @@ struct AttnArgs {
   float* part;
   int H, G, D, Dv, PH, BQ, nsplit, chunk;
   int window, v_col0;          // window <= 0: every earlier key is visible; v_col0: first value column of a pool row
+  int v_hstride;               // columns between the values of neighbouring kv heads (Dv; 0: every kv head reads the
+                               // same Dv value columns, e.g. ALL value heads side by side as one wide head)
   int block;                   // > 0 (and no window): block-diagonal mask, see first_visible
   int head_rows;               // tensor-core kernel, one new token per sequence: the tile's rows are the query HEADS of
                                // one kv head (not tokens), blockIdx.x is a key range, results go to `part`
@@ -103,7 +105,7 @@ __global__ void __launch_bounds__(kWarps * 32) sink_attention_kernel(AttnArgs a)
     }
     for (int i = tid; i < kKeys * Dv; i += blockDim.x) {
       const int j = i / Dv, d = i - j * Dv;
-      vs[i] = j < nk ? to_f32(kv[(int64_t)trow[k0 + j] * a.kv_stride + a.v_col0 + g * Dv + d]) : 0.f;
+      vs[i] = j < nk ? to_f32(kv[(int64_t)trow[k0 + j] * a.kv_stride + a.v_col0 + g * a.v_hstride + d]) : 0.f;
     }
     __syncthreads();
     float sc[kRowsPerWarp];
@@ -279,7 +281,7 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
     for (int j = 0; j < JV; ++j) {
       const int i = tid + 128 * j, r = i / (DVP / 8), c = (i - r * (DVP / 8)) * 8;
       if (rv[j] >= 0 && c < Dv)
-        cp_async_16(smem_u32(vdst + r * VP + c * 2), kv + (int64_t)rv[j] * a.kv_stride + a.v_col0 + g * Dv + c);
+        cp_async_16(smem_u32(vdst + r * VP + c * 2), kv + (int64_t)rv[j] * a.kv_stride + a.v_col0 + g * a.v_hstride + c);
       else
         *reinterpret_cast<uint4*>(vdst + r * VP + c * 2) = make_uint4(0u, 0u, 0u, 0u);
     }
@@ -450,7 +452,7 @@ int dispatch_attention_mma(const AttnArgs& a, int max_q_len, int64_t num_seqs, c
 inline bool mma_path_ok(const AttnArgs& a, int dtype) {
   if (dtype != B2L_F16 && dtype != B2L_BF16) return false;
   if (a.D % 8 || a.Dv % 8 || a.D > 128 || a.Dv > 128) return false;
-  if (a.kv_stride % 8 || a.v_col0 % 8 || a.q_stride % 2 || a.out_stride % 2) return false;
+  if (a.kv_stride % 8 || a.v_col0 % 8 || a.v_hstride % 8 || a.q_stride % 2 || a.out_stride % 2) return false;
   if (((uintptr_t)a.kv % 16) || ((uintptr_t)a.q % 4) || ((uintptr_t)a.out % 4)) return false;
   return true;
 }
@@ -529,7 +531,7 @@ __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
         }
       };
       stage_rows(ks, Dp, g * D, D / VEC);
-      stage_rows(vs, Dvp, a.v_col0 + g * Dv, Dv / VEC);
+      stage_rows(vs, Dvp, a.v_col0 + g * a.v_hstride, Dv / VEC);
     } else {
       for (int i = lane; i < nk * D; i += 32) {
         const int j = i / D, d = i - j * D;
@@ -537,7 +539,7 @@ __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
       }
       for (int i = lane; i < nk * Dv; i += 32) {
         const int j = i / Dv, d = i - j * Dv;
-        vs[j * Dvp + d] = kv[(int64_t)trow[k0 + j] * a.kv_stride + a.v_col0 + g * Dv + d];
+        vs[j * Dvp + d] = kv[(int64_t)trow[k0 + j] * a.kv_stride + a.v_col0 + g * a.v_hstride + d];
       }
     }
     __syncwarp();
@@ -908,14 +910,15 @@ extern "C" int64_t b2l_sink_attention_workspace_bytes(int64_t num_seqs, int head
 /* num_splits == 0: tiled mode over `max_q_len`-token sequences; > 0: split mode, every listed sequence brings ONE token
  * and `split_keys` keys go to each of the num_splits ranges, counted from the token's first visible key
  * (num_splits * split_keys >= the most keys any listed token sees: context + 1, or the window if that is smaller).
- * window <= 0: no sliding window; block > 0 (window <= 0): block-diagonal mask; v_col0 < 0: the values follow the keys in a pool row (column kv_heads * head_dim). */
+ * window <= 0: no sliding window; block > 0 (window <= 0): block-diagonal mask; v_col0 < 0: the values follow the keys in a pool row (column kv_heads * head_dim);
+ * v_head_stride < 0: kv head g's values start g * v_head_dim columns after v_col0 (0: all kv heads read the same columns). */
 extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride,
                                   const void* kv_pool, int64_t kv_row_stride, const void* table_i32,
                                   int64_t table_row_stride, const void* seq_start, const void* seq_ctx,
                                   const void* seq_slot, const void* seq_list, int64_t num_seqs, int max_q_len,
                                   const void* sink, int heads, int kv_heads, int head_dim, int v_head_dim, float scale,
-                                  float softcap, int window, int block, int v_col0, int num_splits,
-                                  int split_keys, void* workspace, int64_t workspace_bytes, int dtype, void* stream) {
+                                  float softcap, int window, int block, int v_col0, int v_head_stride,
+                                  int num_splits, int split_keys, void* workspace, int64_t workspace_bytes, int dtype, void* stream) {
   B2L_REQUIRE(out && q && kv_pool && table_i32 && seq_start && seq_ctx && seq_slot, "sink_attention: null pointer");
   B2L_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "sink_attention: %d heads must be a multiple of num_kv_heads %d",
               heads, kv_heads);
@@ -936,6 +939,7 @@ extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void*
   a.window = window > 0 ? window : 0;
   a.block = (window <= 0 && block > 0) ? block : 0;
   a.v_col0 = v_col0 >= 0 ? v_col0 : kv_heads * head_dim;
+  a.v_hstride = v_head_stride >= 0 ? v_head_stride : v_head_dim;
   a.head_rows = 0;
   const int hchunks = (per + a.PH - 1) / a.PH;
   if (num_splits > 0) {

@@ -1,0 +1,317 @@
+// Linear attention with data-dependent gates over RAGGED steps: per head an fp32 memory S [D x V] kept per request
+// slot, advanced token by token, read out by the query.  Two recurrences share one kernel:
+//
+//   forget-gate (mode 0)   f = l + (1 - l) * sigmoid(z)         per key channel d, lower bound l in [0, 1)
+//                          S[d, :] <- f[d] S[d, :] + (1 - f[d]) v;   o = S^T silu(q)
+//                          (the forget gate also decides what is written: there is no separate key)
+//   gated delta rule (1)   q, k unit vectors (x / sqrt(sum x^2 + unit_eps)), q times q_scale;
+//                          beta = sigmoid(b), g = exp(-exp(A_log) * softplus(a + dt_bias))       per head
+//                          S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+//                          (the read-out sees the current token's write)
+//
+// Thread = one value column of one head: its D memory entries live in registers, so the two contractions over D of a
+// token (S^T k, S^T q) are sums inside a thread and the serial chain of a token has no cross-thread step.  A CTA =
+// (block of value columns, head, sequence) stages 16 tokens at a time: the token's gates, unit norms and scalars are
+// evaluated in fp32 by the warps in parallel and left in shared memory, every thread fetches its own column of v for
+// the 16 tokens, then the 16 updates run back to back.  A sequence without cached tokens starts from zero and never
+// reads its slot; every sequence writes its slot at the end of the step.
+//
+//   head_norm_gate   out[t, h, :] = unit_rms(y[t, h, :]) * w * (silu(gate[t, h, :]) or 1): the per-head output norm
+//                    (weight [V] shared by the heads) with an optional SiLU gate AFTER the norm
+//   head_mix         out[t, h, :] = sum_g M[h, g] * wide[t, g, kv(h), :]: attention weights mixed ACROSS heads after
+//                    the softmax, done on per-head outputs -- head g's weights were applied to every kv head's values
+//                    (sum_j (sum_g M[h,g] p_g(j)) v(j) = sum_g M[h,g] (sum_j p_g(j) v(j)))
+//   swiglu_scaled    out[r, :] = silu(s_r * gate) * (s_r * up) * sigmoid(z_r): a gated activation whose INPUT carries
+//                    a per-row fp32 factor (an expert weight on the expert's input: W (s x) = s (W x)) and whose output
+//                    a per-row logistic gate (both optional)
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float gla_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float gla_silu(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float gla_softplus(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+constexpr int kTok = 16;                  // tokens staged per round
+
+struct GlaArgs {
+  float* y; float* state;
+  const void* q; int64_t q_stride;        // [tokens, QH * D]
+  const void* k; int64_t k_stride;        // mode 1: keys [tokens, QH * D]; mode 0: forget-gate logits [tokens, H * D]
+  const void* v; int64_t v_stride;        // [tokens, H * V]
+  const void* p0; int64_t p0_stride;      // mode 1: write-strength logits [tokens, H]
+  const void* p1; int64_t p1_stride;      // mode 1: decay logits [tokens, H]
+  const void* c0;                         // mode 1: dt_bias [H];  mode 0: lower bounds [H * D]
+  const void* c1;                         // mode 1: A_log [H]
+  const int* seq_start; const int* seq_ctx; const int* seq_slot;
+  int H, QH, D, V;
+  float q_scale, unit_eps;
+};
+
+template <typename T, int DP, int MODE>
+__global__ void __launch_bounds__(128) gated_linear_scan_kernel(GlaArgs a) {
+  pdl_prologue();
+  __shared__ __align__(16) float qs[kTok * DP];
+  __shared__ __align__(16) float ks[kTok * DP];     // mode 1: unit keys; mode 0: forget gates
+  __shared__ float sc[kTok * 2];                    // mode 1: (g, beta) per token
+  const int D = a.D, V = a.V, H = a.H;
+  const int h = blockIdx.y, s = blockIdx.z;
+  const int qh = h / (H / a.QH);
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = col < V;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int start = a.seq_start[s], len = a.seq_start[s + 1] - start, ctx = a.seq_ctx[s];
+  const int64_t slot = a.seq_slot[s];
+  float* sp = a.state + ((slot * H + h) * (int64_t)D) * V;
+  float S[DP];
+#pragma unroll
+  for (int d = 0; d < DP; ++d) S[d] = (ctx > 0 && live && d < D) ? sp[(int64_t)d * V + col] : 0.f;
+  const T* qp = (const T*)a.q;
+  const T* kp = (const T*)a.k;
+  const T* vp = (const T*)a.v;
+  float neg_a = 0.f, dtb = 0.f;
+  if (MODE == 1) { neg_a = -expf(to_f32(((const T*)a.c1)[h])); dtb = to_f32(((const T*)a.c0)[h]); }
+  for (int t0 = 0; t0 < len; t0 += kTok) {
+    const int nt = min(kTok, len - t0);
+    __syncthreads();                                 // the previous round's readers are done
+    for (int t = warp; t < nt; t += nw) {
+      const int64_t row = start + t0 + t;
+      if (MODE == 1) {
+        float qv[DP / 32], kv[DP / 32], sq = 0.f, sk = 0.f;
+#pragma unroll
+        for (int i = 0; i < DP / 32; ++i) {
+          const int d = lane + 32 * i;
+          qv[i] = d < D ? to_f32(qp[row * a.q_stride + qh * D + d]) : 0.f;
+          kv[i] = d < D ? to_f32(kp[row * a.k_stride + qh * D + d]) : 0.f;
+          sq = fmaf(qv[i], qv[i], sq);
+          sk = fmaf(kv[i], kv[i], sk);
+        }
+        const float rq = a.q_scale / sqrtf(warp_reduce_sum(sq) + a.unit_eps);
+        const float rk = 1.0f / sqrtf(warp_reduce_sum(sk) + a.unit_eps);
+#pragma unroll
+        for (int i = 0; i < DP / 32; ++i) {
+          qs[t * DP + lane + 32 * i] = qv[i] * rq;
+          ks[t * DP + lane + 32 * i] = kv[i] * rk;
+        }
+        if (lane == 0) {
+          const float dt = gla_softplus(to_f32(((const T*)a.p1)[row * a.p1_stride + h]) + dtb);
+          sc[2 * t] = expf(neg_a * dt);
+          sc[2 * t + 1] = gla_sigmoid(to_f32(((const T*)a.p0)[row * a.p0_stride + h]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < DP / 32; ++i) {
+          const int d = lane + 32 * i;
+          float qv = 0.f, f = 1.f;                   // rows beyond D: nothing written, nothing read
+          if (d < D) {
+            qv = gla_silu(to_f32(qp[row * a.q_stride + h * D + d]));
+            const float lo = to_f32(((const T*)a.c0)[h * D + d]);
+            f = lo + (1.0f - lo) * gla_sigmoid(to_f32(kp[row * a.k_stride + h * D + d]));
+          }
+          qs[t * DP + d] = qv;
+          ks[t * DP + d] = f;
+        }
+      }
+    }
+    float vr[kTok];
+#pragma unroll
+    for (int t = 0; t < kTok; ++t)
+      vr[t] = (t < nt && live) ? to_f32(vp[(int64_t)(start + t0 + t) * a.v_stride + h * V + col]) : 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int t = 0; t < kTok; ++t) {
+      if (t >= nt) break;
+      const float4* q4 = reinterpret_cast<const float4*>(qs + t * DP);
+      const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP);
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      if (MODE == 1) {
+        const float g = sc[2 * t], beta = sc[2 * t + 1];
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < DP / 4; ++i) {
+          const float4 kk = k4[i];
+          d0 = fmaf(S[4 * i], kk.x, d0); d1 = fmaf(S[4 * i + 1], kk.y, d1);
+          d2 = fmaf(S[4 * i + 2], kk.z, d2); d3 = fmaf(S[4 * i + 3], kk.w, d3);
+        }
+        const float u = beta * (vr[t] - g * ((d0 + d1) + (d2 + d3)));
+#pragma unroll
+        for (int i = 0; i < DP / 4; ++i) {
+          const float4 kk = k4[i], qq = q4[i];
+          S[4 * i] = fmaf(g, S[4 * i], kk.x * u); S[4 * i + 1] = fmaf(g, S[4 * i + 1], kk.y * u);
+          S[4 * i + 2] = fmaf(g, S[4 * i + 2], kk.z * u); S[4 * i + 3] = fmaf(g, S[4 * i + 3], kk.w * u);
+          o0 = fmaf(S[4 * i], qq.x, o0); o1 = fmaf(S[4 * i + 1], qq.y, o1);
+          o2 = fmaf(S[4 * i + 2], qq.z, o2); o3 = fmaf(S[4 * i + 3], qq.w, o3);
+        }
+      } else {
+        const float x = vr[t];
+#pragma unroll
+        for (int i = 0; i < DP / 4; ++i) {
+          const float4 ff = k4[i], qq = q4[i];
+          S[4 * i] = fmaf(ff.x, S[4 * i], (1.0f - ff.x) * x); S[4 * i + 1] = fmaf(ff.y, S[4 * i + 1], (1.0f - ff.y) * x);
+          S[4 * i + 2] = fmaf(ff.z, S[4 * i + 2], (1.0f - ff.z) * x); S[4 * i + 3] = fmaf(ff.w, S[4 * i + 3], (1.0f - ff.w) * x);
+          o0 = fmaf(S[4 * i], qq.x, o0); o1 = fmaf(S[4 * i + 1], qq.y, o1);
+          o2 = fmaf(S[4 * i + 2], qq.z, o2); o3 = fmaf(S[4 * i + 3], qq.w, o3);
+        }
+      }
+      if (live) a.y[(int64_t)(start + t0 + t) * H * V + h * V + col] = (o0 + o1) + (o2 + o3);
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int d = 0; d < DP; ++d)
+      if (d < D) sp[(int64_t)d * V + col] = S[d];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) head_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ y,
+                                                             const T* __restrict__ gate, int64_t gs,
+                                                             const T* __restrict__ w, int heads, int V, float eps) {
+  pdl_prologue();
+  const int64_t t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int h = warp; h < heads; h += nw) {
+    const float* yr = y + (t * heads + h) * (int64_t)V;
+    float ss = 0.f;
+    for (int i = lane; i < V; i += 32) { const float v = yr[i]; ss = fmaf(v, v, ss); }
+    const float rstd = 1.0f / sqrtf(warp_reduce_sum(ss) / (float)V + eps);
+    for (int i = lane; i < V; i += 32) {
+      float v = yr[i] * rstd * to_f32(w[i]);
+      if (gate) v *= gla_silu(to_f32(gate[t * gs + (int64_t)h * V + i]));
+      out[(t * heads + h) * (int64_t)V + i] = from_f32<T>(v);
+    }
+  }
+}
+
+template <typename T>
+__global__ void head_mix_kernel(T* __restrict__ out, const T* __restrict__ wide, int64_t wide_stride,
+                                const T* __restrict__ mix, int heads, int kv_heads, int per_call, int Dv,
+                                int64_t total) {
+  pdl_prologue();
+  const int per = heads / kv_heads;
+  const int64_t call_stride = (int64_t)heads * per_call * Dv;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % Dv);
+    const int h = (int)((idx / Dv) % heads);
+    const int64_t t = idx / ((int64_t)Dv * heads);
+    const int c = h / per;
+    const T* src = wide + t * wide_stride + (c / per_call) * call_stride + (int64_t)(c % per_call) * Dv + i;
+    float acc = 0.f;
+    for (int g = 0; g < heads; ++g) acc = fmaf(to_f32(mix[h * heads + g]), to_f32(src[(int64_t)g * per_call * Dv]), acc);
+    out[idx] = from_f32<T>(acc);
+  }
+}
+
+template <typename T>
+__global__ void swiglu_scaled_kernel(T* __restrict__ out, int64_t os, const T* __restrict__ gate, int64_t gs,
+                                     const T* __restrict__ up, int64_t us, const float* __restrict__ in_scale,
+                                     const T* __restrict__ z, int64_t zs, int64_t n, int64_t total) {
+  pdl_prologue();
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / n, i = idx - r * n;
+    const float s = in_scale ? in_scale[r] : 1.0f;
+    const float g = s * to_f32(gate[r * gs + i]), u = s * to_f32(up[r * us + i]);
+    float v = gla_silu(g) * u;
+    if (z) v *= gla_sigmoid(to_f32(z[r * zs]));
+    out[r * os + i] = from_f32<T>(v);
+  }
+}
+
+template <typename T, int MODE>
+int launch_scan(const GlaArgs& a, int64_t num_seqs, cudaStream_t st) {
+  const int threads = a.V >= 128 ? 128 : ((a.V + 31) / 32) * 32;
+  const dim3 grid((unsigned)((a.V + threads - 1) / threads), (unsigned)a.H, (unsigned)num_seqs);
+#define B2L_GLA(DPV) b2l_launch(gated_linear_scan_kernel<T, DPV, MODE>, grid, dim3(threads), (size_t)0, st, a)
+  if (a.D <= 32) B2L_GLA(32);
+  else if (a.D <= 64) B2L_GLA(64);
+  else if (a.D <= 128) B2L_GLA(128);
+  else B2L_GLA(256);
+#undef B2L_GLA
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+}  // namespace
+
+/* mode 0: forget-gate linear attention (q [tokens, heads*dim] pre-activation, k = forget-gate logits [tokens, heads*dim],
+ * c0 = lower bounds [heads*dim]); mode 1: gated delta rule (q, k [tokens, qk_heads*dim] after their activation, p0 =
+ * write-strength logits, p1 = decay logits [tokens, heads], c0 = dt_bias, c1 = A_log [heads]).  v [tokens, heads*vdim];
+ * y_f32 [tokens, heads*vdim]; state_f32 [slots, heads, dim, vdim] advanced in place. */
+extern "C" int b2l_gated_linear_scan(void* y_f32, void* state_f32, const void* q, int64_t q_row_stride, const void* k,
+                                     int64_t k_row_stride, const void* v, int64_t v_row_stride, const void* p0,
+                                     int64_t p0_row_stride, const void* p1, int64_t p1_row_stride, const void* c0,
+                                     const void* c1, const void* seq_start, const void* seq_ctx, const void* seq_slot,
+                                     int64_t num_seqs, int heads, int qk_heads, int dim, int vdim, float q_scale,
+                                     float unit_eps, int mode, int dtype, void* stream) {
+  B2L_REQUIRE(y_f32 && state_f32 && q && k && v && c0 && seq_start && seq_ctx && seq_slot, "gated_linear_scan: null pointer");
+  B2L_REQUIRE(mode == 0 || (p0 && p1 && c1), "gated_linear_scan: the delta rule needs its gates");
+  B2L_REQUIRE(heads > 0 && qk_heads > 0 && heads % qk_heads == 0 && dim > 0 && dim <= 256 && vdim > 0,
+              "gated_linear_scan: %d heads, %d q/k heads, sizes %d x %d", heads, qk_heads, dim, vdim);
+  B2L_REQUIRE(mode == 1 || qk_heads == heads, "gated_linear_scan: the forget-gate form has one query head per head");
+  if (num_seqs <= 0) return B2L_OK;
+  GlaArgs a;
+  a.y = (float*)y_f32; a.state = (float*)state_f32;
+  a.q = q; a.q_stride = q_row_stride; a.k = k; a.k_stride = k_row_stride; a.v = v; a.v_stride = v_row_stride;
+  a.p0 = p0; a.p0_stride = p0_row_stride; a.p1 = p1; a.p1_stride = p1_row_stride; a.c0 = c0; a.c1 = c1;
+  a.seq_start = (const int*)seq_start; a.seq_ctx = (const int*)seq_ctx; a.seq_slot = (const int*)seq_slot;
+  a.H = heads; a.QH = qk_heads; a.D = dim; a.V = vdim; a.q_scale = q_scale; a.unit_eps = unit_eps;
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = B2L_OK;
+  B2L_DISPATCH_FLOAT(dtype, "gated_linear_scan", {
+    rc = mode == 0 ? launch_scan<T, 0>(a, num_seqs, st) : launch_scan<T, 1>(a, num_seqs, st);
+  });
+  return rc;
+}
+
+extern "C" int b2l_head_norm_gate(void* out, const void* y_f32, const void* gate, int64_t gate_row_stride,
+                                  const void* weight, int64_t rows, int heads, int vdim, float eps, int dtype,
+                                  void* stream) {
+  B2L_REQUIRE(out && y_f32 && weight, "head_norm_gate: null pointer");
+  B2L_REQUIRE(heads > 0 && vdim > 0, "head_norm_gate: bad shape");
+  if (rows <= 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int threads = heads >= 4 ? 128 : heads * 32;
+  B2L_DISPATCH_FLOAT(dtype, "head_norm_gate", {
+    b2l_launch(head_norm_gate_kernel<T>, dim3((unsigned)rows), dim3(threads), (size_t)0, st, (T*)out, (const float*)y_f32,
+               (const T*)gate, gate_row_stride, (const T*)weight, heads, vdim, eps);
+  });
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+/* wide [rows, calls, heads, per_call, vdim] (row stride given): query head g's softmax weights applied to the values of
+ * kv head c lie at call c / per_call, head g, part c % per_call.  out[t, h, :] = sum_g mix[h, g] * wide[t, g, kv(h), :]. */
+extern "C" int b2l_head_mix(void* out, const void* wide, int64_t wide_row_stride, const void* mix, int64_t rows,
+                            int heads, int kv_heads, int per_call, int vdim, int dtype, void* stream) {
+  B2L_REQUIRE(out && wide && mix, "head_mix: null pointer");
+  B2L_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && per_call > 0 && kv_heads % per_call == 0 && vdim > 0,
+              "head_mix: bad shape");
+  if (rows <= 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t total = rows * heads * vdim;
+  const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
+  B2L_DISPATCH_FLOAT(dtype, "head_mix", {
+    b2l_launch(head_mix_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, (const T*)wide, wide_row_stride,
+               (const T*)mix, heads, kv_heads, per_call, vdim, total);
+  });
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+extern "C" int b2l_swiglu_scaled(void* out, int64_t out_row_stride, const void* gate, int64_t gate_row_stride,
+                                 const void* up, int64_t up_row_stride, const void* in_scale_f32, const void* z,
+                                 int64_t z_row_stride, int64_t rows, int64_t n, int dtype, void* stream) {
+  B2L_REQUIRE(out && gate && up, "swiglu_scaled: null pointer");
+  B2L_REQUIRE(n > 0, "swiglu_scaled: bad shape");
+  if (rows <= 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t total = rows * n;
+  const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
+  B2L_DISPATCH_FLOAT(dtype, "swiglu_scaled", {
+    b2l_launch(swiglu_scaled_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, out_row_stride, (const T*)gate,
+               gate_row_stride, (const T*)up, up_row_stride, (const float*)in_scale_f32, (const T*)z, z_row_stride, n,
+               total);
+  });
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}

@@ -151,7 +151,8 @@ __global__ void __launch_bounds__(128) moe_route_sigmoid_kernel(const T* __restr
                                                                 const T* __restrict__ wr, const T* __restrict__ bias,
                                                                 const float* __restrict__ logits, int num_experts,
                                                                 int k, int top_k, int groups, int keep,
-                                                                float* __restrict__ out_w, int* __restrict__ out_ids) {
+                                                                int renormalize, float* __restrict__ out_w,
+                                                                int* __restrict__ out_ids) {
   pdl_prologue();
   extern __shared__ float rs[];
   float* sc = rs;                                // [E] sigmoid scores
@@ -239,6 +240,7 @@ __global__ void __launch_bounds__(128) moe_route_sigmoid_kernel(const T* __restr
     }
   }
   __syncwarp();
+  if (!renormalize) return;                      // the weights stay the winners' own scores
   const float inv = 1.0f / (total + 1e-20f);
   for (int r = lane; r < top_k; r += 32) out_w[(int64_t)t * top_k + r] *= inv;
 }
@@ -297,11 +299,12 @@ extern "C" int b2l_moe_route_topk(void* topk_weights, void* topk_ids_i64, const 
 
 /* Sigmoid scores + selection bias + group-limited top-k (fp32 throughout).  The router product is done here from
  * x [tokens, k] and router_w [experts, k] in dtype, unless logits_f32 [tokens, experts] brings it; bias [experts] in
- * dtype (nullable); weights_f32 [tokens, top_k], ids_i32 [tokens, top_k].  groups must divide experts; keep <= groups. */
+ * dtype (nullable); weights_f32 [tokens, top_k], ids_i32 [tokens, top_k].  groups must divide experts; keep <= groups.
+ * renormalize 0: the weights are the winners' scores themselves, not divided by their sum. */
 extern "C" int b2l_moe_route_sigmoid_groups(void* weights_f32, void* ids_i32, const void* x, int64_t x_row_stride,
                                             const void* router_w, const void* bias, const void* logits_f32,
                                             int64_t tokens, int num_experts, int64_t k, int top_k, int groups, int keep,
-                                            int dtype, void* stream) {
+                                            int renormalize, int dtype, void* stream) {
   B2L_REQUIRE(weights_f32 && ids_i32 && ((x && router_w) || logits_f32), "moe_route_sigmoid_groups: null pointer");
   B2L_REQUIRE(num_experts > 0 && k > 0 && k < (1ll << 31) && top_k >= 1 && top_k <= num_experts && groups >= 1 &&
                   num_experts % groups == 0 && keep >= 1 && keep <= groups &&
@@ -314,7 +317,7 @@ extern "C" int b2l_moe_route_sigmoid_groups(void* weights_f32, void* ids_i32, co
   B2L_DISPATCH_FLOAT(dtype, "moe_route_sigmoid_groups", {
     b2l_launch(moe_route_sigmoid_kernel<T>, dim3((unsigned)tokens), dim3(logits_f32 ? 32 : 128), smem, st, (const T*)x,
                x_row_stride, (const T*)router_w, (const T*)bias, (const float*)logits_f32, num_experts, (int)k, top_k,
-               groups, keep, (float*)weights_f32, (int*)ids_i32);
+               groups, keep, renormalize, (float*)weights_f32, (int*)ids_i32);
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;

@@ -4,7 +4,7 @@
 //   * depth_mix_norms       x = sum_j c_j X_j over the kept results (or x = X_last when c == NULL), written as the next
 //                           level of the stack, and, from the same statistic, the two input norms of a parallel block:
 //                           h1 = unit_rms(x) * (offset + w1), h2 = unit_rms(x) * (offset + w2)            (in T)
-//   * branch_sum_residual   x += s * (a' + b') + c, where a' = unit_rms(a) * wa when wa is given, else a (b' likewise;
+//   * branch_sum_residual   x += s * a' + s_b * b' + c, where a' = unit_rms(a) * wa when wa is given, else a (b' likewise;
 //                           b and c optional): a mixer with one or two normed branches plus a feed-forward output
 //                           joining the residual in one pass; optional copy of the new x in T for the next GEMM
 //   * gelu_mul_gather       o[t, d] = gelu_tanh(z[t, d]) * table[token[t], col0 + d]       (per-layer token input)
@@ -154,8 +154,9 @@ __global__ void __launch_bounds__(256) branch_sum_residual_kernel(float* __restr
                                                                   const T* __restrict__ a, int64_t as,
                                                                   const T* __restrict__ wa, const T* __restrict__ b,
                                                                   int64_t bs, const T* __restrict__ wb,
-                                                                  const T* __restrict__ c, int64_t cs, int64_t n,
-                                                                  float eps, float scale, int vec) {
+                                                                  const T* __restrict__ c, int64_t cs,
+                                                                  const T* __restrict__ wn, int64_t n, float eps,
+                                                                  float scale, float scale_b, int vec) {
   pdl_prologue();
   __shared__ float red[32];
   const int64_t t = blockIdx.x;
@@ -183,6 +184,7 @@ __global__ void __launch_bounds__(256) branch_sum_residual_kernel(float* __restr
       if (wa) ra = 1.0f / sqrtf(block_sum_ps(sa, red) / (float)n + eps);
       if (br && wb) rb = 1.0f / sqrtf(block_sum_ps(sb, red) / (float)n + eps);
     }
+    float sn = 0.f;
     for (int64_t i = (int64_t)threadIdx.x * 4; i < n; i += (int64_t)blockDim.x * 4) {
       float m[4], g[4], x[4];
       row_load4(ar + i, m);
@@ -191,19 +193,19 @@ __global__ void __launch_bounds__(256) branch_sum_residual_kernel(float* __restr
 #pragma unroll
         for (int k = 0; k < 4; ++k) m[k] = m[k] * ra * g[k];
       }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) m[k] *= scale;
       if (br) {
         row_load4(br + i, x);
         if (wb) {
           row_load4(wb + i, g);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) m[k] += x[k] * rb * g[k];
+          for (int k = 0; k < 4; ++k) m[k] = fmaf(x[k] * rb * g[k], scale_b, m[k]);
         } else {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) m[k] += x[k];
+          for (int k = 0; k < 4; ++k) m[k] = fmaf(x[k], scale_b, m[k]);
         }
       }
-#pragma unroll
-      for (int k = 0; k < 4; ++k) m[k] *= scale;
       if (cr) {
         row_load4(cr + i, x);
 #pragma unroll
@@ -211,9 +213,20 @@ __global__ void __launch_bounds__(256) branch_sum_residual_kernel(float* __restr
       }
       row_load4(r + t * n + i, x);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) m[k] += x[k];
+      for (int k = 0; k < 4; ++k) { m[k] += x[k]; sn = fmaf(m[k], m[k], sn); }
       row_store4(r + t * n + i, m);
-      if (act) row_store4(act + t * n + i, m);
+      if (act && !wn) row_store4(act + t * n + i, m);
+    }
+    if (act && wn) {                         // the next block's input norm of the new residual (own stores re-read)
+      const float rn = 1.0f / sqrtf(block_sum_ps(sn, red) / (float)n + eps);
+      for (int64_t i = (int64_t)threadIdx.x * 4; i < n; i += (int64_t)blockDim.x * 4) {
+        float m[4], g[4];
+        row_load4(r + t * n + i, m);
+        row_load4(wn + i, g);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) m[k] = m[k] * rn * g[k];
+        row_store4(act + t * n + i, m);
+      }
     }
     return;
   }
@@ -227,19 +240,26 @@ __global__ void __launch_bounds__(256) branch_sum_residual_kernel(float* __restr
     for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_f32(br[i]); ss = fmaf(v, v, ss); }
     rb = 1.0f / sqrtf(block_sum_ps(ss, red) / (float)n + eps);
   }
+  float sn = 0.f;
   for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
     float m = to_f32(ar[i]) * ra;
     if (wa) m *= to_f32(wa[i]);
+    m *= scale;
     if (br) {
       float m2 = to_f32(br[i]) * rb;
       if (wb) m2 *= to_f32(wb[i]);
-      m += m2;
+      m = fmaf(m2, scale_b, m);
     }
-    m *= scale;
     if (cr) m += to_f32(cr[i]);
     const float v = r[t * n + i] + m;
     r[t * n + i] = v;
-    if (act) act[t * n + i] = from_f32<T>(v);
+    sn = fmaf(v, v, sn);
+    if (act && !wn) act[t * n + i] = from_f32<T>(v);
+  }
+  if (act && wn) {
+    const float rn = 1.0f / sqrtf(block_sum_ps(sn, red) / (float)n + eps);
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x)
+      act[t * n + i] = from_f32<T>(r[t * n + i] * rn * to_f32(wn[i]));
   }
 }
 
@@ -307,8 +327,8 @@ extern "C" int b2l_depth_mix_norms(void* x_out_f32, void* h1, void* h2, const vo
 
 extern "C" int b2l_branch_sum_residual(void* residual_f32, void* act, const void* a, int64_t a_row_stride,
                                        const void* a_weight, const void* b, int64_t b_row_stride, const void* b_weight,
-                                       const void* c, int64_t c_row_stride, int64_t rows, int64_t n, float eps,
-                                       float scale, int dtype, void* stream) {
+                                       const void* c, int64_t c_row_stride, const void* next_weight, int64_t rows,
+                                       int64_t n, float eps, float scale, float scale_b, int dtype, void* stream) {
   B2L_REQUIRE(residual_f32 && a, "branch_sum_residual: null pointer");
   B2L_REQUIRE(rows >= 0 && n > 0, "branch_sum_residual: bad shape");
   if (rows == 0) return B2L_OK;
@@ -316,8 +336,8 @@ extern "C" int b2l_branch_sum_residual(void* residual_f32, void* act, const void
   B2L_DISPATCH_FLOAT(dtype, "branch_sum_residual", {
     b2l_launch(branch_sum_residual_kernel<T>, dim3((unsigned)rows), dim3(256), (size_t)0, st, (float*)residual_f32,
                (T*)act, (const T*)a, a_row_stride, (const T*)a_weight, (const T*)b, b_row_stride, (const T*)b_weight,
-               (const T*)c, c_row_stride, n, eps, scale,
-               (int)(n % 4 == 0 && a_row_stride % 4 == 0 && b_row_stride % 4 == 0 && c_row_stride % 4 == 0 &&
+               (const T*)c, c_row_stride, (const T*)next_weight, n, eps, scale, scale_b,
+               (int)(n % 4 == 0 && row_aligned4<T>(next_weight) && a_row_stride % 4 == 0 && b_row_stride % 4 == 0 && c_row_stride % 4 == 0 &&
                      row_aligned4<T>(a) && row_aligned4<T>(b) && row_aligned4<T>(c) && row_aligned4<T>(a_weight) &&
                      row_aligned4<T>(b_weight) && row_aligned4<T>(act) && (uintptr_t)residual_f32 % 16 == 0));
   });

@@ -5,7 +5,7 @@
 //                          and, fused, the NEXT sublayer's input norm: act = norm'(r) * w'   (pre+post-norm designs)
 //   * rmsnorm_from_f32     o = norm(r) * (offset + w), selected rows                    (input norm / final norm)
 //   * relu_squared, gelu   o = max(x, 0)^2;  o = gelu(x), exact (erf) or tanh form
-//   * softcap_to_f32       o = cap * tanh(x / cap) as fp32 (cap <= 0: plain copy)       (logits)
+//   * softcap_to_f32       o = cap * tanh(s x / cap) as fp32 (cap <= 0: s x)            (logits)
 // norm = x / sqrt(mean(x^2) + eps) (kind 0, RMS) or (x - mean) / sqrt(mean((x - mean)^2) + eps) (kind 1, layer norm
 // without bias; the variance is taken from the deviations in a pass of its own).
 // `offset` = 1 for weights stored around zero, 0 for plain weights.  All statistics in fp32.
@@ -218,11 +218,12 @@ __global__ void gelu_kernel(T* __restrict__ o, const T* __restrict__ x, int64_t 
 }
 
 template <typename T>
-__global__ void softcap_to_f32_kernel(float* __restrict__ o, const T* __restrict__ x, int64_t total, float cap) {
+__global__ void softcap_to_f32_kernel(float* __restrict__ o, const T* __restrict__ x, int64_t total, float cap,
+                                      float scale) {
   pdl_prologue();
   const float inv = cap > 0.f ? 1.0f / cap : 0.f;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const float v = to_f32(x[i]);
+    const float v = to_f32(x[i]) * scale;
     o[i] = cap > 0.f ? cap * tanhf(v * inv) : v;
   }
 }
@@ -333,13 +334,15 @@ extern "C" int b2l_gelu(void* out, const void* x, int64_t total, int tanh_form, 
   return B2L_OK;
 }
 
-extern "C" int b2l_softcap_to_f32(void* out_f32, const void* x, int64_t total, float cap, int dtype, void* stream) {
+extern "C" int b2l_softcap_to_f32(void* out_f32, const void* x, int64_t total, float cap, float scale, int dtype,
+                                  void* stream) {
   B2L_REQUIRE(out_f32 && x, "softcap_to_f32: null pointer");
   if (total <= 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
   B2L_DISPATCH_FLOAT(dtype, "softcap_to_f32", {
-    b2l_launch(softcap_to_f32_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (float*)out_f32, (const T*)x, total, cap);
+    b2l_launch(softcap_to_f32_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (float*)out_f32, (const T*)x, total, cap,
+               scale);
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;

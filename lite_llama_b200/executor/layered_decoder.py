@@ -46,11 +46,14 @@ from ..kernels import (
     embed_positions,
     embed_rmsnorm,
     gated_group_norm,
+    gated_linear_scan,
     gated_scan,
     gelu,
     gelu_mul_gather,
     grouped_experts,
     head_linear,
+    head_mix,
+    head_norm_gate,
     head_norm_rope_prepare,
     latent_prepare,
     linear,
@@ -67,9 +70,11 @@ from ..kernels import (
     softcap_to_f32,
     ssm_scan,
     swiglu_forward,
+    swiglu_scaled,
 )
-from .model_config import (BlockAttentionSpec, DecayAttentionSpec, DenseMlpSpec, LatentAttentionSpec, LayeredConfig,
-                           LayerSpec, Mamba2Spec, MinGruSpec, MoeMlpSpec, RgLruSpec, SideBySideSpec, SinkAttentionSpec)
+from .model_config import (BlockAttentionSpec, ConvWindowAttentionSpec, DecayAttentionSpec, DeltaRuleSpec, DenseMlpSpec,
+                           ForgetGateAttentionSpec, LatentAttentionSpec, LayeredConfig, LayerSpec, Mamba2Spec,
+                           MinGruSpec, MoeMlpSpec, RgLruSpec, SideBySideSpec, SinkAttentionSpec, WindowDeltaPairSpec)
 from .ragged_batch import RaggedBatch
 from .registry import Architecture, register
 
@@ -143,14 +148,15 @@ class StepContext:
 
 @dataclass
 class Branches:
-    """A mixer's output as up to two branches that the residual kernel norms (plain weights) and averages:
-    ``scale * (unit_rms(a) * a_weight + unit_rms(b) * b_weight)``."""
+    """A mixer's output as up to two branches that the residual kernel norms (plain weights; none: the branch as it
+    is) and sums: ``scale * unit_rms(a) * a_weight + scale_b * unit_rms(b) * b_weight``."""
 
     a: torch.Tensor
     a_weight: torch.Tensor | None
     b: torch.Tensor | None = None
     b_weight: torch.Tensor | None = None
     scale: float = 1.0
+    scale_b: float | None = None                       # the second branch's own factor (default: ``scale``)
 
 
 def mamba2_mixer(li: int, spec: Mamba2Spec, w: dict[str, torch.Tensor], x: torch.Tensor, ctx: StepContext,
@@ -309,6 +315,89 @@ def side_by_side_mixer(li: int, spec: SideBySideSpec, w: dict[str, torch.Tensor]
     return Branches(left, w["left_out"], right, w["right_out"], 0.5)
 
 
+def forget_gate_mixer(li: int, spec: ForgetGateAttentionSpec, w: dict[str, torch.Tensor], x: torch.Tensor,
+                      ctx: StepContext, eps: float) -> torch.Tensor:
+    """ONE projection [q | forget-gate logits (biased) | v] -> the recurrence against the slot's fp32 memory (SiLU of q,
+    the bounded forget gate and its complement evaluated in fp32 inside the kernel) -> per-head RMS norm ->
+    out-projection."""
+    b, n = ctx.batch, spec.heads * spec.head_dim
+    proj = linear(x, w["in"], w["in_b"])
+    y = gated_linear_scan("forget_gate", ctx.states.ssm_state[li], proj[:, :n], proj[:, n:2 * n], proj[:, 2 * n:],
+                          b.seq_start, b.seq_ctx, b.seq_slot, spec.heads, spec.heads, spec.head_dim, spec.v_head_dim,
+                          c0=w["lower"])
+    return linear(head_norm_gate(y, w["norm"], spec.heads, eps), w["o"])
+
+
+def wide_value_heads(spec: ConvWindowAttentionSpec, sixteen_bit: bool) -> int:
+    """How many kv heads' values one attention call reads side by side as one wide value head when the softmax
+    weights are mixed across heads: the most that divide ``kv_heads`` and stay inside the kernels' value width (128
+    columns on the tensor-core tiles, 256 on the CUDA cores)."""
+    limit = 128 if sixteen_bit and spec.head_dim % 8 == 0 and spec.v_head_dim % 8 == 0 and spec.head_dim <= 128 else 256
+    best = 1
+    for c in range(1, spec.kv_heads + 1):
+        if spec.kv_heads % c == 0 and c * spec.v_head_dim <= limit:
+            best = c
+    return best
+
+
+def conv_window_attention(li: int, spec: ConvWindowAttentionSpec, w: dict[str, torch.Tensor], proj: torch.Tensor,
+                          ctx: StepContext, eps: float) -> torch.Tensor:
+    """The attention half of ``window_delta_mixer`` from the fused projection's leading columns [q | k | v]: the short
+    convolution (tail per slot), unit-RMS of q and k per head and the cache write, attention under the window, the
+    head mix.  Mixing the heads' softmax weights is linear in the weights, so it is done on OUTPUTS: every query head's
+    weights are applied to the values of every kv head (the value heads of a pool row read side by side as one wide
+    head, ``v_head_stride = 0``), and ``head_mix`` forms ``sum_g M[h, g] * out[g, kv(h)]``."""
+    b, L = ctx.batch, spec
+    H, G, D, Dv = L.heads, L.kv_heads, L.head_dim, L.v_head_dim
+    pool = ctx.kv_buffer[li]
+    qkv = causal_conv_silu(proj, 0, L.channels, w["left_conv"], w["left_conv_b"], ctx.states.named_tail[li]["left"],
+                           b.seq_start, b.seq_ctx, b.seq_slot, activation=False)
+    ones = w["ones"] if L.qk_unit_rms else None
+    head_norm_rope_prepare(qkv, pool, b.kv_rows, None, ones, ones, H, G, D, Dv, 0, eps)
+    per_call = wide_value_heads(L, qkv.dtype != torch.float32) if L.head_mix else 0
+    calls = G // per_call if L.head_mix else 1
+    width = per_call * Dv if L.head_mix else Dv
+    att = torch.empty((b.tokens, calls * H * width), dtype=qkv.dtype, device=qkv.device)
+    for c in range(calls):
+        out = att[:, c * H * width:(c + 1) * H * width]
+        extra = {"v_col0": G * D + c * width, "v_head_stride": 0} if L.head_mix else {}
+        common = (H, G, D, width, L.scale, 0.0)
+        if b.num_portions:
+            sink_attention(out, qkv, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.portion_list, b.num_portions,
+                           b.max_portion, None, *common, window=L.window, **extra)
+        if b.num_singles:
+            keys = b.max_single_ctx + 1
+            splits, per = split_plan(min(keys, L.window) if L.window else keys)
+            sink_attention(out, qkv, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.single_list, b.num_singles,
+                           1, None, *common, num_splits=splits, split_keys=per, window=L.window, **extra)
+    if L.head_mix:
+        att = head_mix(att, w["talk"], H, G, per_call, Dv)
+    return linear(att, w["left_o"])
+
+
+def window_delta_mixer(li: int, spec: WindowDeltaPairSpec, w: dict[str, torch.Tensor], x: torch.Tensor,
+                       ctx: StepContext, eps: float) -> Branches:
+    """ONE projection for both halves, [q | k | v (biased) | pad || q' | k' | v' | write logits | decay logits | pad ||
+    gate'].  Left: ``conv_window_attention``.  Right: convolution + SiLU of q', k', v' (tail per slot), the gated delta
+    rule against the slot's fp32 memory (unit norms, write strength and decay in fp32 inside the kernel), per-head RMS
+    norm times the SiLU gate, out-projection.  The residual kernel scales and sums the two."""
+    b, L, R = ctx.batch, spec.left, spec.right
+    proj = linear(x, w["in"], w["in_b"])
+    left = conv_window_attention(li, L, w, proj, ctx, eps)
+    r0 = -(-L.channels // 8) * 8
+    nqk, nv = R.qk_heads * R.head_dim, R.heads * R.v_head_dim
+    qkv = causal_conv_silu(proj, r0, R.channels, w["right_conv"], w["right_conv_b"], ctx.states.named_tail[li]["right"],
+                           b.seq_start, b.seq_ctx, b.seq_slot)
+    p0 = r0 + R.channels
+    g0 = r0 + -(-(R.channels + 2 * R.heads) // 8) * 8
+    y = gated_linear_scan("delta_rule", ctx.states.ssm_state[li], qkv[:, :nqk], qkv[:, nqk:2 * nqk], qkv[:, 2 * nqk:],
+                          b.seq_start, b.seq_ctx, b.seq_slot, R.heads, R.qk_heads, R.head_dim, R.v_head_dim,
+                          c0=w["dt_bias"], c1=w["A_log"], p0=proj[:, p0:p0 + R.heads],
+                          p1=proj[:, p0 + R.heads:p0 + 2 * R.heads], q_scale=R.head_dim ** -0.5, unit_eps=R.unit_eps)
+    right = linear(head_norm_gate(y, w["right_norm"], R.heads, eps, proj[:, g0:g0 + nv]), w["right_o"])
+    return Branches(left, None, right, None, spec.left_scale, spec.right_scale)
+
+
 def spec_magnitude(spec: BlockAttentionSpec) -> float:
     return rotary_frequencies(spec.rot_dims, spec.rot_base, spec.rot_factor, spec.rot_original, spec.rot_fast,
                               spec.rot_slow)[1]
@@ -336,15 +425,26 @@ def dense_feed_forward(spec: DenseMlpSpec, w: dict[str, torch.Tensor], x: torch.
 def moe_feed_forward(spec: MoeMlpSpec, w: dict[str, torch.Tensor], x: torch.Tensor) -> torch.Tensor:
     """Router (product, sigmoid, bias, group-limited top-k: one launch) -> the shared expert as two dense products ->
     the routed experts as two grouped products; the shared expert's output joins the weighted sum in its kernel."""
-    weights, ids = route_sigmoid_groups(x, w["router"], w.get("correction"), spec.top, spec.groups, spec.keep)
+    weights, ids = route_sigmoid_groups(x, w["router"], w.get("correction"), spec.top, spec.groups, spec.keep,
+                                        renormalize=spec.renormalize)
     shared = None
+    if spec.gated:
+        # gated experts: [gate | up] stacked per expert; the shared expert's [gate | up | token-gate row] is one product
+        if spec.shared_ff:
+            f = spec.shared_ff
+            gu = linear(x, w["shared_gate_up"])
+            z = gu[:, 2 * f:2 * f + 1] if spec.shared_gate else None
+            shared = linear(swiglu_scaled(gu[:, :f], gu[:, f:2 * f], None, z), w["shared_down"])
+        return grouped_experts(x, w["gate_up"], w["down"], weights, ids, addend=shared, activation=spec.activation,
+                               gated=True, weight_on_input=spec.weight_on_input)
     if spec.shared_ff:
         shared = linear(_activate(spec.activation, linear(x, w["shared_up"])), w["shared_down"])
     return grouped_experts(x, w["up"], w["down"], weights, ids, addend=shared, activation=spec.activation)
 
 
 MIXERS = {"mamba2": mamba2_mixer, "attention": sink_attention_mixer, "latent_attention": latent_attention_mixer,
-          "mingru": min_gru_mixer, "rglru": rg_lru_mixer, "parallel": side_by_side_mixer}
+          "mingru": min_gru_mixer, "rglru": rg_lru_mixer, "parallel": side_by_side_mixer,
+          "forget_gate": forget_gate_mixer, "window_delta": window_delta_mixer}
 FEED_FORWARDS = {"dense": dense_feed_forward, "moe": moe_feed_forward}
 
 
@@ -363,6 +463,8 @@ class LayeredDecoder:
         design soft-caps its logits)."""
         cfg, eps, off, kind = self.cfg, self.cfg.rms_norm_eps, self.norm_offset, self.cfg.norm_kind
         ctx = StepContext(batch, kv_buffer, table, states)
+        if cfg.single_norm:
+            return self._forward_single_norm(tokens, ctx, want_rows)
         if cfg.parallel_block:
             return self._forward_parallel(tokens, ctx, want_rows)
         pre = cfg.pre_norm
@@ -396,7 +498,32 @@ class LayeredDecoder:
         cfg = self.cfg
         hidden = rmsnorm_from_f32(resid, self.w.final_norm, cfg.rms_norm_eps, self.norm_offset, want_rows, cfg.norm_kind)
         logits = linear(hidden, self.w.head)
-        return softcap_to_f32(logits, cfg.logit_softcap) if cfg.logit_softcap else logits
+        if cfg.logit_softcap or cfg.logit_scale != 1.0:
+            return softcap_to_f32(logits, cfg.logit_softcap, cfg.logit_scale)
+        return logits
+
+    def _forward_single_norm(self, tokens: torch.Tensor, ctx: StepContext, want_rows: torch.Tensor | None) -> torch.Tensor:
+        """Parallel blocks with one norm: ``h = norm1(x)``; ``x <- x + mixer(h) + ff(h)``.  The residual stays fp32 in
+        place; one kernel adds the (scaled) mixer branches and the feed-forward output and hands out the NEXT layer's
+        ``h`` from the same pass."""
+        cfg, w, eps, off = self.cfg, self.w, self.cfg.rms_norm_eps, self.norm_offset
+        if cfg.norm_kind != "rms" or off != 0.0:
+            raise ValueError("single-norm parallel blocks use plain RMS norms")
+        resid, _ = embed_positions(tokens, ctx.batch.positions, w.embed, w.pos, want_act=False, scale=cfg.embed_scale)
+        count = len(cfg.layers)
+        h = rmsnorm_from_f32(resid, w.layers[0].pre1, eps, off, None, cfg.norm_kind) if count else None
+        for li, (spec, lw) in enumerate(zip(cfg.layers, w.layers)):
+            y = MIXERS[spec.kind](li, spec.mixer, lw.mix, h, ctx, eps)
+            f = FEED_FORWARDS[spec.mlp.kind](spec.mlp, lw.mlp, h) if spec.mlp is not None else None
+            br = y if isinstance(y, Branches) else Branches(y, None)
+            nxt = w.layers[li + 1].pre1 if li + 1 < count else None
+            h = branch_sum_residual(resid, br.a, br.a_weight, br.b, br.b_weight, f, eps, br.scale, want_act=False,
+                                    scale_b=br.scale_b, next_weight=nxt)
+            if self.layer_trace is not None:
+                self.layer_trace.append(resid.clone())
+        if want_rows is not None and want_rows.numel() == 0:
+            return torch.empty((0, cfg.vocab_size), dtype=torch.float32, device=tokens.device)
+        return self._head(resid, want_rows)
 
     def _forward_parallel(self, tokens: torch.Tensor, ctx: StepContext, want_rows: torch.Tensor | None) -> torch.Tensor:
         """Parallel blocks over a stack of fp32 results: level 0 is the (normed) embedding, level i + 1 the result of
@@ -426,7 +553,7 @@ class LayeredDecoder:
             f = FEED_FORWARDS[spec.mlp.kind](spec.mlp, lw.mlp, h2) if spec.mlp is not None else None
             br = y if isinstance(y, Branches) else Branches(y, None)
             act = branch_sum_residual(x, br.a, br.a_weight, br.b, br.b_weight, f, eps, br.scale,
-                                      want_act=lw.side is not None)
+                                      want_act=lw.side is not None, scale_b=br.scale_b)
             if lw.side is not None:
                 d = cfg.token_side_dim
                 z = linear(x if act is None else act, lw.side["gate"])
@@ -861,3 +988,182 @@ _TISOSUN_SOURCES = ("gemm_dense", "gemm_simt", "gemm_rows_mma", "residual_stream
                     "rotary_heads", "ssm_scan", "decay_attention_mma", "attention_sink", "elementwise")
 register(Architecture("Tisosun", parse_tisosun_config, map_tisosun_weights, LayeredDecoder, ragged_steps=True,
                       sources=_TISOSUN_SOURCES))
+
+
+# ---------------------------------------------------------------------------------------------- Gofezen plumbing #
+def _gofezen_mlp(mlp: dict | None) -> DenseMlpSpec | MoeMlpSpec | None:
+    if mlp is None:
+        return None
+    kind = mlp.get("kind", "dense")
+    if kind == "dense":
+        return DenseMlpSpec(ff=int(mlp["ff"]), activation="silu", gated=True)
+    if kind != "moe":
+        raise ValueError(f"unknown feed-forward kind {kind!r}")
+    r = mlp["router"]
+    shared = mlp.get("shared") or {}
+    return MoeMlpSpec(experts=int(r["experts"]), top=int(r["top"]), ff=int(mlp["expert"]["ff"]),
+                      shared_ff=int(shared.get("ff", 0)), activation="silu", gated=True, renormalize=False,
+                      weight_on_input=True, shared_gate=bool(shared))
+
+
+def parse_gofezen_config(raw: dict) -> LayeredConfig:
+    layers = []
+    for entry in raw["layers"]:
+        kind, m = entry["type"], entry["mixer"]
+        if kind == "hgrn2":
+            key, mixer = "forget_gate", ForgetGateAttentionSpec(heads=int(m["heads"]), head_dim=int(m["dim"]),
+                                                                v_head_dim=int(m.get("vdim", m["dim"])))
+        elif kind == "parallel":
+            l, r = m["left"], m["right"]
+            left = ConvWindowAttentionSpec(heads=int(l["heads"]), kv_heads=int(l.get("kv_heads", l["heads"])),
+                                           head_dim=int(l["dim"]), v_head_dim=int(l.get("vdim", l["dim"])),
+                                           scale=float(l["scale"]), window=int((l.get("mask") or {}).get("size", 0)),
+                                           conv=int(l.get("conv", 1)))
+            right = DeltaRuleSpec(heads=int(r["heads"]), qk_heads=int(r.get("kv_heads", r["heads"])),
+                                  head_dim=int(r["dim"]), v_head_dim=int(r.get("vdim", r["dim"])),
+                                  conv=int(r.get("conv", 1)))
+            key, mixer = "window_delta", WindowDeltaPairSpec(left, right, float(m.get("left_scale", 1.0)),
+                                                             float(m.get("right_scale", 1.0)))
+        else:
+            raise ValueError(f"unknown layer type {kind!r}")
+        layers.append(LayerSpec(key, mixer, _gofezen_mlp(entry.get("mlp"))))
+    return LayeredConfig(name=raw.get("architecture", "Gofezen"), hidden_size=int(raw["width"]),
+                         vocab_size=int(raw["vocab"]), max_seq_len=int(raw["max_positions"]),
+                         rms_norm_eps=float(raw["norm"]["eps"]), layers=tuple(layers), norm_weight_offset=0.0,
+                         embed_scale=float((raw.get("embedding") or {}).get("scale", 1.0)),
+                         logit_softcap=float(raw.get("logit_softcap") or 0.0), parallel_block=True, single_norm=True,
+                         logit_scale=float(raw.get("logit_scale", 1.0)))
+
+
+def map_gofezen_weights(cfg: LayeredConfig, tensors: dict[str, torch.Tensor], device: str,
+                        dtype: torch.dtype) -> LayeredWeights:
+    """Checkpoint names -> the decoder's weights.  Every mixer's input projections are row-concatenated into one GEMM
+    weight with one bias vector (zeros where a projection has none); parts that a kernel reads with 16-byte accesses
+    start on a multiple of 8 rows.  The convolutions' tap tables are stacked in the same order as their channels.
+    Experts are stacked with each expert's gate rows before its up rows; the shared expert's token-gate row rides at
+    the end of its [gate | up] weight."""
+
+    def get(name: str) -> torch.Tensor:
+        if name not in tensors:
+            raise KeyError(f"checkpoint has no tensor {name!r}")
+        return tensors[name].to(device=device, dtype=dtype).contiguous()
+
+    def zeros(*shape: int) -> torch.Tensor:
+        return torch.zeros(shape, dtype=dtype, device=device)
+
+    out = LayeredWeights(embed=get("embed"), pos=get("pos"), final_norm=get("final.norm"), head=get("head"))
+    for i, spec in enumerate(cfg.layers):
+        p, m = f"l{i}.mix.", spec.mixer
+        if isinstance(m, ForgetGateAttentionSpec):
+            n = m.heads * m.head_dim
+            mix = {"in": torch.cat([get(p + "q"), get(p + "f"), get(p + "v")], dim=0).contiguous(),
+                   "in_b": torch.cat([zeros(n), get(p + "f.b"), zeros(m.heads * m.v_head_dim)]),
+                   "lower": get(p + "lower"), "norm": get(p + "norm"), "o": get(p + "o")}
+        else:
+            L, R = m.left, m.right
+            lq = _pad_rows(torch.cat([get(p + "left.q"), get(p + "left.k"), get(p + "left.v")], dim=0), 8)
+            lb = _pad_rows(torch.cat([get(p + "left.q.b"), get(p + "left.k.b"), get(p + "left.v.b")]), 8)
+            rq = _pad_rows(torch.cat([get(p + "right.q"), get(p + "right.k"), get(p + "right.v"), get(p + "right.b"),
+                                      get(p + "right.a")], dim=0), 8)
+            rg = _pad_rows(get(p + "right.g"), 8)
+            mix = {"in": torch.cat([lq, rq, rg], dim=0).contiguous(),
+                   "in_b": torch.cat([lb, zeros(rq.shape[0] + rg.shape[0])]),
+                   "left_conv": torch.cat([get(p + "left.q.conv"), get(p + "left.k.conv"), get(p + "left.v.conv")],
+                                          dim=0).contiguous(),
+                   "left_conv_b": zeros(L.channels), "ones": torch.ones(L.head_dim, dtype=dtype, device=device),
+                   "left_o": get(p + "left.o"),
+                   "right_conv": torch.cat([get(p + "right.q.conv"), get(p + "right.k.conv"), get(p + "right.v.conv")],
+                                           dim=0).contiguous(),
+                   "right_conv_b": zeros(R.channels), "A_log": get(p + "right.A_log"), "dt_bias": get(p + "right.dt_bias"),
+                   "right_norm": get(p + "right.norm"), "right_o": get(p + "right.o")}
+            if L.head_mix:
+                mix["talk"] = get(p + "left.talk")
+        lw = LayeredLayerWeights(norm1=None, mix=mix, pre1=get(f"l{i}.norm1"))
+        q = f"l{i}.mlp."
+        if isinstance(spec.mlp, DenseMlpSpec):
+            lw.mlp = {"gate_up": torch.cat([get(q + "gate"), get(q + "up")], dim=0).contiguous(), "down": get(q + "down")}
+        elif isinstance(spec.mlp, MoeMlpSpec):
+            e = range(spec.mlp.experts)
+            lw.mlp = {"router": get(q + "router"),
+                      "gate_up": torch.stack([torch.cat([get(f"{q}e{j}.gate"), get(f"{q}e{j}.up")], dim=0) for j in e]).contiguous(),
+                      "down": torch.stack([get(f"{q}e{j}.down") for j in e]).contiguous()}
+            if spec.mlp.shared_ff:
+                parts = [get(q + "shared.gate"), get(q + "shared.up")]
+                if spec.mlp.shared_gate:
+                    parts.append(get(q + "shared.sg").reshape(1, -1))
+                lw.mlp["shared_gate_up"] = _pad_rows(torch.cat(parts, dim=0), 8).contiguous()
+                lw.mlp["shared_down"] = get(q + "shared.down")
+        out.layers.append(lw)
+    return out
+
+
+def gofezen_tensor_shapes(cfg: LayeredConfig) -> dict[str, tuple[int, ...]]:
+    """Checkpoint tensor names and shapes of a configuration (random initialisation, shape checks)."""
+    w = cfg.hidden_size
+    shapes: dict[str, tuple[int, ...]] = {"embed": (cfg.vocab_size, w), "pos": (cfg.max_seq_len, w)}
+    for i, spec in enumerate(cfg.layers):
+        p, m = f"l{i}.mix.", spec.mixer
+        shapes[f"l{i}.norm1"] = (w,)
+        if isinstance(m, ForgetGateAttentionSpec):
+            n, nv = m.heads * m.head_dim, m.heads * m.v_head_dim
+            shapes.update({p + "q": (n, w), p + "f": (n, w), p + "f.b": (n,), p + "lower": (n,), p + "v": (nv, w),
+                           p + "norm": (m.v_head_dim,), p + "o": (w, nv)})
+        else:
+            L, R = m.left, m.right
+            lq, lk, lv = L.heads * L.head_dim, L.kv_heads * L.head_dim, L.kv_heads * L.v_head_dim
+            rq, rv = R.qk_heads * R.head_dim, R.heads * R.v_head_dim
+            shapes.update({p + "left.q": (lq, w), p + "left.q.b": (lq,), p + "left.k": (lk, w), p + "left.k.b": (lk,),
+                           p + "left.v": (lv, w), p + "left.v.b": (lv,), p + "left.q.conv": (lq, L.conv),
+                           p + "left.k.conv": (lk, L.conv), p + "left.v.conv": (lv, L.conv),
+                           p + "left.talk": (L.heads, L.heads), p + "left.o": (w, L.heads * L.v_head_dim),
+                           p + "right.q": (rq, w), p + "right.q.conv": (rq, R.conv), p + "right.k": (rq, w),
+                           p + "right.k.conv": (rq, R.conv), p + "right.v": (rv, w), p + "right.v.conv": (rv, R.conv),
+                           p + "right.b": (R.heads, w), p + "right.A_log": (R.heads,), p + "right.norm": (R.v_head_dim,),
+                           p + "right.a": (R.heads, w), p + "right.dt_bias": (R.heads,), p + "right.g": (rv, w),
+                           p + "right.o": (w, rv)})
+        q = f"l{i}.mlp."
+        if isinstance(spec.mlp, DenseMlpSpec):
+            shapes.update({q + "gate": (spec.mlp.ff, w), q + "up": (spec.mlp.ff, w), q + "down": (w, spec.mlp.ff)})
+        elif isinstance(spec.mlp, MoeMlpSpec):
+            for e in range(spec.mlp.experts):
+                shapes.update({f"{q}e{e}.gate": (spec.mlp.ff, w), f"{q}e{e}.up": (spec.mlp.ff, w),
+                               f"{q}e{e}.down": (w, spec.mlp.ff)})
+            shapes[q + "router"] = (spec.mlp.experts, w)
+            if spec.mlp.shared_ff:
+                f = spec.mlp.shared_ff
+                shapes.update({q + "shared.gate": (f, w), q + "shared.up": (f, w), q + "shared.down": (w, f),
+                               q + "shared.sg": (1, w)})
+    shapes.update({"final.norm": (w,), "head": (cfg.vocab_size, w)})
+    return shapes
+
+
+def random_gofezen_tensors(cfg: LayeredConfig, seed: int = 0) -> dict[str, torch.Tensor]:
+    """Seeded random bf16 tensors with checkpoint names (benchmarks and tests; no trained checkpoints exist offline)."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in gofezen_tensor_shapes(cfg).items():
+        leaf = name.rsplit(".", 1)[-1]
+        if leaf == "conv":
+            t = 0.4 * torch.randn(shape, generator=g)
+        elif leaf == "talk":                                  # mostly the head itself, some of every other head
+            t = 0.2 * torch.randn(shape, generator=g) + 0.8 * torch.eye(shape[0])
+        elif leaf == "lower":
+            t = torch.rand(shape, generator=g) * 0.9
+        elif name == "pos":
+            t = 0.5 * torch.randn(shape, generator=g)
+        elif len(shape) == 2:
+            t = torch.randn(shape, generator=g) / (shape[1] ** 0.5)
+        elif leaf in ("A_log", "dt_bias"):
+            t = -1.0 + 0.7 * torch.randn(shape, generator=g)
+        elif leaf == "b" and name.endswith((".q.b", ".k.b", ".v.b", ".f.b")):
+            t = 0.3 * torch.randn(shape, generator=g)
+        else:                                                 # plain norm weights
+            t = 1.0 + 0.1 * torch.randn(shape, generator=g)
+        out[name] = t.to(torch.bfloat16)
+    return out
+
+
+_GOFEZEN_SOURCES = ("gemm_dense", "gemm_simt", "gemm_rows_mma", "residual_stream", "parallel_stream", "ssm_scan",
+                    "gated_linear_attention", "rotary_heads", "attention_sink", "moe_routing", "elementwise")
+register(Architecture("Gofezen", parse_gofezen_config, map_gofezen_weights, LayeredDecoder, ragged_steps=True,
+                      sources=_GOFEZEN_SOURCES))

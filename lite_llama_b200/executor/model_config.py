@@ -291,6 +291,121 @@ class SideBySideSpec:
 
 
 @dataclass(frozen=True)
+class ForgetGateAttentionSpec:
+    """Linear attention whose forget gate also decides what is written: per head an fp32 memory ``head_dim x
+    v_head_dim``; per key channel ``f = l + (1 - l) sigmoid(.)`` with a learned lower bound ``l``;
+    ``S <- diag(f) S + (1 - f) v^T``, read-out ``S^T silu(q)``, per-head RMS norm (one ``[v_head_dim]`` weight)."""
+
+    heads: int
+    head_dim: int
+    v_head_dim: int
+
+    @property
+    def state_shape(self) -> tuple[int, ...]:
+        return (self.heads, self.head_dim, self.v_head_dim)
+
+    conv_tail_shape = None
+
+    def validate(self) -> None:
+        if min(self.heads, self.head_dim, self.v_head_dim) < 1 or self.head_dim > 256:
+            raise ValueError(f"unsupported linear attention geometry: {self}")
+
+
+@dataclass(frozen=True)
+class ConvWindowAttentionSpec:
+    """Position-free softmax attention: biased projections, a ``conv``-tap causal convolution on q, k and v (no
+    activation), a weightless per-head unit-RMS of q and k (``qk_unit_rms``), a sliding ``window`` (0: plain causal)
+    and, with ``head_mix``, a ``heads x heads`` matrix that mixes the heads' softmax weights before they meet the
+    values (every head keeps reading its own key/value head)."""
+
+    heads: int
+    kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    scale: float
+    window: int = 0
+    conv: int = 1
+    head_mix: bool = True
+    qk_unit_rms: bool = True
+
+    @property
+    def channels(self) -> int:                         # q | k | v side by side: what the convolution runs over
+        return self.heads * self.head_dim + self.kv_heads * (self.head_dim + self.v_head_dim)
+
+    @property
+    def cache_row_width(self) -> int:                  # all K heads, then all V heads, padded to 16-byte vectors
+        return -(-self.kv_heads * (self.head_dim + self.v_head_dim) // 8) * 8
+
+    def validate(self) -> None:
+        if min(self.heads, self.kv_heads, self.head_dim, self.v_head_dim, self.conv) < 1 or self.heads % self.kv_heads \
+                or self.v_head_dim > 256 or self.window < 0:
+            raise ValueError(f"unsupported attention geometry: {self}")
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """Gated delta rule: q, k (``qk_heads x head_dim``) and v (``heads x v_head_dim``) pass a ``conv``-tap causal
+    convolution and SiLU; q, k become unit vectors (``unit_eps`` inside the root), q times ``head_dim^-1/2``; per head a
+    write strength ``sigmoid(.)`` and a decay ``exp(-exp(A_log) softplus(. + dt_bias))``;
+    ``S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``; per-head RMS norm, SiLU gate."""
+
+    heads: int
+    qk_heads: int
+    head_dim: int
+    v_head_dim: int
+    conv: int = 1
+    unit_eps: float = 1e-6
+
+    @property
+    def channels(self) -> int:
+        return 2 * self.qk_heads * self.head_dim + self.heads * self.v_head_dim
+
+    @property
+    def state_shape(self) -> tuple[int, ...]:
+        return (self.heads, self.head_dim, self.v_head_dim)
+
+    def validate(self) -> None:
+        if min(self.heads, self.qk_heads, self.head_dim, self.v_head_dim, self.conv) < 1 or self.heads % self.qk_heads \
+                or self.head_dim > 256:
+            raise ValueError(f"unsupported delta-rule geometry: {self}")
+
+
+@dataclass(frozen=True)
+class WindowDeltaPairSpec:
+    """Two mixers that read the same input: convolved sliding-window attention over the KV pool (``left``) and a gated
+    delta rule over a state slot (``right``); the result is ``left_scale * left + right_scale * right``.  Each side
+    keeps the last inputs of its own convolution per slot (``conv_tails``)."""
+
+    left: ConvWindowAttentionSpec
+    right: DeltaRuleSpec
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+
+    def validate(self) -> None:
+        self.left.validate()
+        self.right.validate()
+
+    @property
+    def cache_row_width(self) -> int:
+        return self.left.cache_row_width
+
+    @property
+    def window(self) -> int:
+        return self.left.window
+
+    @property
+    def state_shape(self) -> tuple[int, ...]:
+        return self.right.state_shape
+
+    conv_tail_shape = None
+
+    @property
+    def conv_tails(self) -> dict[str, tuple[int, int]]:       # per request slot, activation dtype
+        return {"left": (max(self.left.conv - 1, 1), self.left.channels),
+                "right": (max(self.right.conv - 1, 1), self.right.channels)}
+
+
+@dataclass(frozen=True)
 class DenseMlpSpec:
     ff: int
     activation: str = "relu2"                          # "relu2" | "gelu" | "gelu_tanh"; gated: "silu"
@@ -300,10 +415,12 @@ class DenseMlpSpec:
 
 @dataclass(frozen=True)
 class MoeMlpSpec:
-    """Routed ungated experts ``W_down act(W_up h)`` + an optional shared one that every token uses.  Sigmoid router
-    scores; the choice adds a per-expert selection bias; ``groups`` runs of neighbouring experts compete with the sum
-    of their two best choice scores and only the ``keep`` best groups are eligible; the ``top`` winners' weights are
-    their scores over the winners' sum."""
+    """Routed experts ``W_down act(W_up h)`` (``gated``: ``W_down (act(W_gate h) * W_up h)``) + an optional shared one
+    that every token uses.  Sigmoid router scores; the choice adds a per-expert selection bias; ``groups`` runs of
+    neighbouring experts compete with the sum of their two best choice scores and only the ``keep`` best groups are
+    eligible; the ``top`` winners' weights are their scores over the winners' sum, or (``renormalize=False``) the
+    scores themselves.  ``weight_on_input``: an expert sees the token TIMES its weight instead of having its output
+    weighted.  ``shared_gate``: the shared expert's output is scaled by one logistic number per token."""
 
     experts: int
     top: int
@@ -313,6 +430,10 @@ class MoeMlpSpec:
     shared_ff: int = 0
     activation: str = "gelu"
     kind: str = "moe"
+    gated: bool = False
+    renormalize: bool = True
+    weight_on_input: bool = False
+    shared_gate: bool = False
 
     def validate(self) -> None:
         if self.experts < 1 or not 1 <= self.top <= self.experts or self.groups < 1 or self.experts % self.groups or \
@@ -351,6 +472,9 @@ class LayeredConfig:
     embed_norm: bool = False
     token_side_dim: int = 0
     depth_average: bool = False
+    # single_norm: a parallel block with ONE input norm that both sublayers read, x <- x + mixer(h) + ff(h), h = norm1(x)
+    single_norm: bool = False
+    logit_scale: float = 1.0                           # the head's output times this, before the soft cap
 
     @property
     def num_layers(self) -> int:

@@ -8,6 +8,7 @@ hand-written sm_100a CUDA from ``libb200lite.so`` on the current CUDA stream.
 from .flashattention2_nopad import flash_attention2_no_pad
 from .flashdecoding import flash_decoding
 from .fused_moe import fused_moe, grouped_experts, moe_align_block_size, route_sigmoid_groups, route_topk
+from .gated_linear import gated_linear_scan, head_mix, head_norm_gate, swiglu_scaled
 from .latent import head_linear, latent_prepare, rope_heads, rope_table
 from .linear import linear, linear_simt
 from .parallel_stream import branch_sum_residual, depth_mix_norms, embed_rmsnorm, gelu_mul_gather
@@ -30,6 +31,10 @@ __all__ = [
     "moe_align_block_size",
     "route_topk",
     "route_sigmoid_groups",
+    "gated_linear_scan",
+    "head_norm_gate",
+    "head_mix",
+    "swiglu_scaled",
     "grouped_experts",
     "head_linear",
     "latent_prepare",

@@ -169,12 +169,12 @@ def route_topk(router_logits: torch.Tensor, top_k: int, renormalize: bool = True
 
 @torch.no_grad()
 def route_sigmoid_groups(x: torch.Tensor, router_w: torch.Tensor, bias: torch.Tensor | None, top_k: int,
-                         groups: int = 1, keep: int = 1):
+                         groups: int = 1, keep: int = 1, renormalize: bool = True):
     """Sigmoid router with a selection bias and group-limited choice (router product with fp32 results + one selection
     launch; a single launch for shapes no GEMM takes):
     ``s = sigmoid(router_w @ x)`` in fp32; experts compete with ``s + bias``; they form ``groups`` runs of neighbours,
     a group scores the sum of its two best, only the ``keep`` best groups are eligible; the ``top_k`` winners' weights
-    are their ``s`` over the winners' sum.  Returns ``(weights fp32 [T, k], ids int32 [T, k])``.  The reference's
+    are their ``s`` over the winners' sum (``renormalize=False``: their ``s`` as they are).  Returns ``(weights fp32 [T, k], ids int32 [T, k])``.  The reference's
     router is a softmax over all experts (lite_llama/models/qwen3_moe.py:94-100, ``route_topk``)."""
     require_cuda(x, router_w, bias)
     if x.stride(-1) != 1:
@@ -199,26 +199,39 @@ def route_sigmoid_groups(x: torch.Tensor, router_w: torch.Tensor, bias: torch.Te
         check(L.b2l_linear_f32out_mma(logits.data_ptr(), x.data_ptr(), router_w.data_ptr(), tokens, e, k, x.stride(0), e,
                                       code, stream_handle()))
     check(L.b2l_moe_route_sigmoid_groups(w.data_ptr(), ids.data_ptr(), x.data_ptr(), x.stride(0), router_w.data_ptr(),
-                                         ptr(bias), ptr(logits), tokens, e, k, int(top_k), int(groups), int(keep), code,
+                                         ptr(bias), ptr(logits), tokens, e, k, int(top_k), int(groups), int(keep), 1 if renormalize else 0, code,
                                          stream_handle()))
     return w, ids
 
 
+def _swiglu_into(mid: torch.Tensor, wide: torch.Tensor, ff: int, in_scale: torch.Tensor | None) -> None:
+    """``mid = silu(s * wide[:, :ff]) * (s * wide[:, ff:])`` with the per-slot fp32 factor ``s`` (optional)."""
+    check(lib().b2l_swiglu_scaled(mid.data_ptr(), mid.stride(0), wide.data_ptr(), wide.stride(0), wide[:, ff:].data_ptr(),
+                                  wide.stride(0), ptr(in_scale), None, 0, mid.shape[0], ff, float_code(mid, "mid"),
+                                  stream_handle()))
+
+
 @torch.no_grad()
 def grouped_experts(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, weights: torch.Tensor,
-                    ids: torch.Tensor, addend: torch.Tensor | None = None, activation: str = "gelu") -> torch.Tensor:
+                    ids: torch.Tensor, addend: torch.Tensor | None = None, activation: str = "gelu",
+                    gated: bool = False, weight_on_input: bool = False) -> torch.Tensor:
     """``sum_k weights[t, k] * W_down[e] act(W_up[e] x[t]) (+ addend[t])`` over each token's chosen experts
     ``e = ids[t, k]``: ungated two-matrix experts, ``w_up [E, ff, h]``, ``w_down [E, h, ff]``.  Slots are sorted by
     expert (``moe_align_block_size``), both products run grouped (``mma.sync`` tiles for aligned 16-bit operands, the
     CUDA cores for true fp32 and odd shapes) with the activation in the first one's epilogue and the fp32 routing weight
-    in the second's.  The gated (SwiGLU) experts of the reference's family are ``fused_moe``."""
+    in the second's.  ``gated`` (``activation="silu"``): ``w_up [E, 2 * ff, h]`` holds every expert's gate rows then its
+    up rows, and the unit is ``W_down (silu(W_gate x) * W_up x)``; the activation is a kernel of its own between the
+    products.  ``weight_on_input``: the expert sees ``weights[t, k] * x[t]`` and its output is not weighted; the factor
+    passes through the first (linear) product and is applied to its fp32-widened results.  The fp16 / fp8 gated experts
+    of the reference's family are ``fused_moe``."""
     require_cuda(x, w_up, w_down, weights, ids, addend)
-    if activation != "gelu":
-        raise ValueError(f"grouped_experts: unknown activation {activation!r}")
+    if (activation, gated) not in (("gelu", False), ("silu", True)) or (weight_on_input and not gated):
+        raise ValueError(f"grouped_experts: unknown expert form {activation!r}, gated={gated}")
     if weights.dtype != torch.float32:
         raise ValueError("grouped_experts: routing weights are fp32")
     tokens, hidden = x.shape
-    num_experts, ff, _ = w_up.shape
+    num_experts, up_rows, _ = w_up.shape
+    ff = up_rows // 2 if gated else up_rows
     top_k = ids.shape[1]
     L = lib()
     code = float_code(x, "x")
@@ -227,8 +240,11 @@ def grouped_experts(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, w
     w_up, w_down = w_up.contiguous(), w_down.contiguous()
     slots = tokens * top_k
     mid = torch.empty((slots, ff), dtype=x.dtype, device=x.device)
+    wide = torch.empty((slots, up_rows), dtype=x.dtype, device=x.device) if gated else mid
     expanded = torch.empty((slots, hidden), dtype=x.dtype, device=x.device)
     flat_w = weights.reshape(-1).contiguous()
+    down_w = None if weight_on_input else flat_w.data_ptr()
+    act = 0 if gated else 1
     # 16-bit operands with 16-byte aligned rows run on the tensor cores (blocks of 16, 64 or 128 slots by the expected
     # slots per expert), everything else on the CUDA cores; the result of a slot does not depend on the block size
     tensor = bool(L.b2l_rows_gemm_mma_ok(x.data_ptr(), w_up.data_ptr(), hidden, x.stride(0), 0, code)) and \
@@ -237,15 +253,22 @@ def grouped_experts(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, w
     block = (16 if per_expert <= 16 else (64 if per_expert <= 256 else 128)) if tensor else L.b2l_moe_gemm_simt_block()
     sorted_ids, expert_ids, num_post = moe_align_block_size(ids, block, num_experts)
     common = (sorted_ids.data_ptr(), expert_ids.data_ptr(), num_post.data_ptr(), sorted_ids.numel(), slots)
+
+    def between() -> None:
+        if gated:
+            _swiglu_into(mid, wide, ff, flat_w if weight_on_input else None)
+
     if tensor:
-        check(L.b2l_moe_gemm_mma(mid.data_ptr(), x.data_ptr(), w_up.data_ptr(), None, *common, top_k, block, ff, hidden,
-                                 x.stride(0), mid.stride(0), 1, code, stream_handle()))
-        check(L.b2l_moe_gemm_mma(expanded.data_ptr(), mid.data_ptr(), w_down.data_ptr(), flat_w.data_ptr(), *common, 1,
+        check(L.b2l_moe_gemm_mma(wide.data_ptr(), x.data_ptr(), w_up.data_ptr(), None, *common, top_k, block, up_rows,
+                                 hidden, x.stride(0), wide.stride(0), act, code, stream_handle()))
+        between()
+        check(L.b2l_moe_gemm_mma(expanded.data_ptr(), mid.data_ptr(), w_down.data_ptr(), down_w, *common, 1,
                                  block, hidden, ff, mid.stride(0), expanded.stride(0), 0, code, stream_handle()))
     else:
-        check(L.b2l_moe_gemm_simt(mid.data_ptr(), x.data_ptr(), w_up.data_ptr(), None, *common, top_k, ff, hidden,
-                                  x.stride(0), mid.stride(0), 1, code, stream_handle()))
-        check(L.b2l_moe_gemm_simt(expanded.data_ptr(), mid.data_ptr(), w_down.data_ptr(), flat_w.data_ptr(), *common, 1,
+        check(L.b2l_moe_gemm_simt(wide.data_ptr(), x.data_ptr(), w_up.data_ptr(), None, *common, top_k, up_rows, hidden,
+                                  x.stride(0), wide.stride(0), act, code, stream_handle()))
+        between()
+        check(L.b2l_moe_gemm_simt(expanded.data_ptr(), mid.data_ptr(), w_down.data_ptr(), down_w, *common, 1,
                                   hidden, ff, mid.stride(0), expanded.stride(0), 0, code, stream_handle()))
     out = torch.empty((tokens, hidden), dtype=x.dtype, device=x.device)
     check(L.b2l_moe_sum(out.data_ptr(), expanded.data_ptr(), ptr(addend), tokens, hidden, top_k, code, stream_handle()))

@@ -63,25 +63,31 @@ def depth_mix_norms(stack: torch.Tensor, count: int, coef: torch.Tensor | None, 
 def branch_sum_residual(residual: torch.Tensor, a: torch.Tensor, a_weight: torch.Tensor | None = None,
                         b: torch.Tensor | None = None, b_weight: torch.Tensor | None = None,
                         c: torch.Tensor | None = None, eps: float = 0.0, scale: float = 1.0,
-                        want_act: bool = True) -> torch.Tensor | None:
-    """``residual += scale * (a' + b') + c`` in place (fp32), where ``a' = unit_rms(a) * a_weight`` when the weight is
-    given, else ``a`` (``b`` likewise; ``b`` and ``c`` optional).  Returns the new residual in ``a``'s dtype for the
-    next projection (``None`` for fp32 or ``want_act=False``)."""
-    require_cuda(residual, a, a_weight, b, b_weight, c)
+                        want_act: bool = True, scale_b: float | None = None,
+                        next_weight: torch.Tensor | None = None) -> torch.Tensor | None:
+    """``residual += scale * a' + scale_b * b' + c`` in place (fp32), where ``a' = unit_rms(a) * a_weight`` when the
+    weight is given, else ``a`` (``b`` likewise; ``b`` and ``c`` optional; ``scale_b`` defaults to ``scale``).  Returns
+    the new residual in ``a``'s dtype for the next projection (``None`` for fp32 or ``want_act=False``); with
+    ``next_weight`` it returns ``unit_rms(new residual) * next_weight`` instead, the input norm of the block that
+    follows, in every dtype."""
+    require_cuda(residual, a, a_weight, b, b_weight, c, next_weight)
     if residual.dtype != torch.float32 or not residual.is_contiguous():
         raise ValueError("branch_sum_residual: the residual stream is a contiguous fp32 tensor")
     rows, n = residual.shape
     for t in (a, b, c):
         if t is not None and (t.shape != residual.shape or t.stride(-1) != 1 or t.dtype != a.dtype):
             raise ValueError("branch_sum_residual: the branches match the residual's shape and share one dtype")
-    for t in (a_weight, b_weight):
+    for t in (a_weight, b_weight, next_weight):
         if t is not None and (t.dtype != a.dtype or t.numel() != n):
             raise ValueError("branch_sum_residual: norm weights are [n] in the branches' dtype")
-    act = torch.empty((rows, n), dtype=a.dtype, device=a.device) if want_act and a.dtype != torch.float32 else None
+    act = None
+    if next_weight is not None or (want_act and a.dtype != torch.float32):
+        act = torch.empty((rows, n), dtype=a.dtype, device=a.device)
     check(lib().b2l_branch_sum_residual(residual.data_ptr(), ptr(act), a.data_ptr(), a.stride(0), ptr(a_weight), ptr(b),
                                         b.stride(0) if b is not None else 0, ptr(b_weight), ptr(c),
-                                        c.stride(0) if c is not None else 0, rows, n, float(eps), float(scale),
-                                        float_code(a, "a"), stream_handle()))
+                                        c.stride(0) if c is not None else 0, ptr(next_weight), rows, n, float(eps),
+                                        float(scale), float(scale if scale_b is None else scale_b), float_code(a, "a"),
+                                        stream_handle()))
     return act
 
 

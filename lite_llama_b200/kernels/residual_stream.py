@@ -95,11 +95,12 @@ def gelu(x: torch.Tensor, approximate: str = "none") -> torch.Tensor:
 
 
 @torch.no_grad()
-def softcap_to_f32(x: torch.Tensor, cap: float) -> torch.Tensor:
-    """``cap * tanh(x / cap)`` as fp32 (``cap <= 0``: a plain fp32 copy): the logits a soft-capped head hands out."""
+def softcap_to_f32(x: torch.Tensor, cap: float, scale: float = 1.0) -> torch.Tensor:
+    """``cap * tanh(scale * x / cap)`` as fp32 (``cap <= 0``: ``scale * x``): the logits a scaled, soft-capped head
+    hands out."""
     require_cuda(x)
     x = x if x.is_contiguous() else x.contiguous()
     out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
-    check(lib().b2l_softcap_to_f32(out.data_ptr(), x.data_ptr(), x.numel(), float(cap or 0.0), float_code(x, "x"),
+    check(lib().b2l_softcap_to_f32(out.data_ptr(), x.data_ptr(), x.numel(), float(cap or 0.0), float(scale), float_code(x, "x"),
                                    stream_handle()))
     return out
