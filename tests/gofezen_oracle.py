@@ -158,8 +158,12 @@ def layer_tensors(tensors: dict, i: int, part: str) -> dict:
     return {k[len(p):]: f64(v) for k, v in tensors.items() if k.startswith(p)}
 
 
-def forward(config: dict, tensors: dict, tokens, trace: list | None = None) -> np.ndarray:
-    """``tokens`` of ONE sequence -> logits ``[T, vocab]``; ``trace`` collects the residual after every layer."""
+def forward(config: dict, tensors: dict, tokens, trace: list | None = None, return_layers: bool = False):
+    """``tokens`` of ONE sequence -> logits ``[T, vocab]``; ``trace`` collects the residual after every layer
+    (``return_layers``: returned beside the logits)."""
+    if return_layers:
+        layers: list = []
+        return forward(config, tensors, tokens, layers), layers
     eps = float(config["norm"]["eps"])
     T = len(tokens)
     x = f64(tensors["embed"])[list(tokens)] * float((config.get("embedding") or {}).get("scale", 1.0))
@@ -185,3 +189,113 @@ def forward(config: dict, tensors: dict, tokens, trace: list | None = None) -> n
     z = np.stack([unit_rms(r, eps) * fn for r in x]) @ f64(tensors["head"]).T * float(config.get("logit_scale", 1.0))
     cap = float(config.get("logit_softcap") or 0.0)
     return cap * np.tanh(z / cap) if cap else z
+
+
+# ------------------------------------------------------------------------------------------- test model builders #
+def left_entry(heads=3, kv_heads=1, dim=6, vdim=5, size=9, conv=3, scale=0.4) -> dict:
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": size}, "conv": conv,
+            "scale": scale}
+
+
+def right_entry(heads=2, kv_heads=1, dim=4, vdim=6, conv=2) -> dict:
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}
+
+
+def dense_mlp(ff=14) -> dict:
+    return {"kind": "dense", "ff": ff}
+
+
+def moe_mlp(experts=5, top=2, ff=6, shared_ff=7) -> dict:
+    out = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}}
+    if shared_ff:
+        out["shared"] = {"ff": shared_ff}
+    return out
+
+
+def hgrn2_layer(heads=2, dim=4, vdim=6, mlp="dense") -> dict:
+    return {"type": "hgrn2", "mixer": {"heads": heads, "dim": dim, "vdim": vdim},
+            "mlp": dense_mlp() if mlp == "dense" else mlp}
+
+
+def pair_layer(left=None, right=None, left_scale=0.6, right_scale=0.9, mlp="moe") -> dict:
+    return {"type": "parallel", "mixer": {"left": left or left_entry(), "right": right or right_entry(),
+                                          "left_scale": left_scale, "right_scale": right_scale},
+            "mlp": moe_mlp() if mlp == "moe" else mlp}
+
+
+def make_config(layers, width=24, vocab=50, eps=1e-5, embed_scale=3.0, logit_scale=0.7, softcap=12.0,
+                max_positions=512) -> dict:
+    return {"architecture": "Gofezen", "width": width, "vocab": vocab, "max_positions": max_positions,
+            "norm": {"eps": eps}, "embedding": {"scale": embed_scale}, "logit_scale": logit_scale,
+            "logit_softcap": softcap, "layers": list(layers)}
+
+
+def tensor_shapes(config: dict) -> dict:
+    w = config["width"]
+    out = {"embed": (config["vocab"], w), "pos": (config["max_positions"], w), "final.norm": (w,),
+           "head": (config["vocab"], w)}
+    for i, layer in enumerate(config["layers"]):
+        p, m = f"l{i}.mix.", layer["mixer"]
+        out[f"l{i}.norm1"] = (w,)
+        if layer["type"] == "hgrn2":
+            n, nv = m["heads"] * m["dim"], m["heads"] * m["vdim"]
+            out.update({p + "q": (n, w), p + "f": (n, w), p + "f.b": (n,), p + "lower": (n,), p + "v": (nv, w),
+                        p + "norm": (m["vdim"],), p + "o": (w, nv)})
+        else:
+            a, b = m["left"], m["right"]
+            for name, rows in (("q", a["heads"] * a["dim"]), ("k", a["kv_heads"] * a["dim"]), ("v", a["kv_heads"] * a["vdim"])):
+                out.update({f"{p}left.{name}": (rows, w), f"{p}left.{name}.b": (rows,), f"{p}left.{name}.conv": (rows, a["conv"])})
+            out.update({p + "left.talk": (a["heads"], a["heads"]), p + "left.o": (w, a["heads"] * a["vdim"])})
+            for name, rows in (("q", b["kv_heads"] * b["dim"]), ("k", b["kv_heads"] * b["dim"]), ("v", b["heads"] * b["vdim"])):
+                out.update({f"{p}right.{name}": (rows, w), f"{p}right.{name}.conv": (rows, b["conv"])})
+            out.update({p + "right.b": (b["heads"], w), p + "right.a": (b["heads"], w), p + "right.A_log": (b["heads"],),
+                        p + "right.dt_bias": (b["heads"],), p + "right.norm": (b["vdim"],),
+                        p + "right.g": (b["heads"] * b["vdim"], w), p + "right.o": (w, b["heads"] * b["vdim"])})
+        mlp, q = layer.get("mlp"), f"l{i}.mlp."
+        if mlp is None:
+            continue
+        if mlp["kind"] == "dense":
+            out.update({q + "gate": (mlp["ff"], w), q + "up": (mlp["ff"], w), q + "down": (w, mlp["ff"])})
+        else:
+            f = mlp["expert"]["ff"]
+            for e in range(mlp["router"]["experts"]):
+                out.update({f"{q}e{e}.gate": (f, w), f"{q}e{e}.up": (f, w), f"{q}e{e}.down": (w, f)})
+            out[q + "router"] = (mlp["router"]["experts"], w)
+            if mlp.get("shared"):
+                f = mlp["shared"]["ff"]
+                out.update({q + "shared.gate": (f, w), q + "shared.up": (f, w), q + "shared.down": (w, f),
+                            q + "shared.sg": (1, w)})
+    return out
+
+
+def random_model(config: dict, seed: int = 0, spread: float = 1.0) -> dict:
+    """Random tensors (torch, fp32 holding bf16-exact values) with checkpoint names; ``spread`` widens the head so
+    that greedy choices are decided by more than rounding."""
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(config).items():
+        leaf = name.rsplit(".", 1)[-1]
+        if leaf == "conv":
+            t = 0.5 * torch.randn(shape, generator=g)
+        elif leaf == "talk":
+            t = 0.3 * torch.randn(shape, generator=g) + 0.7 * torch.eye(shape[0])
+        elif leaf == "lower":
+            t = 0.9 * torch.rand(shape, generator=g)
+        elif name == "pos":
+            t = 0.5 * torch.randn(shape, generator=g)
+        elif name == "head":
+            t = spread * torch.randn(shape, generator=g) / shape[1] ** 0.5
+        elif leaf == "router":
+            t = 3.0 * torch.randn(shape, generator=g) / shape[1] ** 0.5
+        elif len(shape) == 2:
+            t = torch.randn(shape, generator=g) / shape[1] ** 0.5
+        elif leaf in ("A_log", "dt_bias"):
+            t = -1.0 + 0.8 * torch.randn(shape, generator=g)
+        elif leaf == "b":
+            t = 0.3 * torch.randn(shape, generator=g)
+        else:
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        out[name] = t.to(torch.bfloat16).float()
+    return out
