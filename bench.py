@@ -40,7 +40,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--design", default=None, choices=["gufotar", "pesivik", "tisosun"],
+    ap.add_argument("--design", default=None, choices=["gufotar", "pesivik", "tisosun", "gofezen"],
                     help="instead of the headline workload: prefill / decode throughput and per-kernel rooflines of a "
                          "layer-list design beside the closest uniform decoder (bench_design.py); 1 GPU")
     ap.add_argument("--design-sizes", default=None, help="comma-separated subset of bench_design.SIZES")

@@ -1,7 +1,8 @@
-"""``bench.py --design gufotar | pesivik | tisosun``: prefill and decode throughput of a layer-list design at a few sizes that resemble
+"""``bench.py --design gufotar | pesivik | tisosun | gofezen``: prefill and decode throughput of a layer-list design at a few sizes that resemble
 a real model's layers (random weights, synthetic ids), beside the closest existing model of the framework (the
 uniform rotary decoder: same width, layer count, attention geometry and feed-forward width; for Tisosun the Gufotar
-layer-list model, the other design with recurrent layers beside attention layers), plus every kernel of the
+layer-list model, the other design with recurrent layers beside attention layers; for Gofezen the Tisosun model, the
+other design of parallel blocks), plus every kernel of the
 new path timed alone against its like kernel with the fraction of the measured roofline each reaches.
 
 Timing: CUDA events on the launching stream, >= 3 warm-up runs, a 256 MiB write between timed runs (larger than the
@@ -781,6 +782,287 @@ def tisosun_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) 
     return rows
 
 
+G_SIZES = {
+    # attention half: heads x head_dim on kv_heads under a sliding window; delta-rule half: r_heads memories of r_dim x
+    # r_vdim on r_qk query/key heads; forget-gate layers: f_heads memories of f_dim x f_vdim; a dense gated feed-forward in
+    # the forget-gate layers, routed experts (+ a shared one) in the side-by-side layers.  The Tisosun columns are its
+    # own geometry at equal width, depth, attention shape and dense feed-forward width.
+    "small": dict(width=1024, layers=4, heads=16, kv_heads=4, head_dim=64, window=256, r_heads=16, r_qk=4, r_dim=64,
+                  r_vdim=64, f_heads=8, f_dim=128, f_vdim=128, ff=2048, experts=16, top=2, e_ff=512, shared=1024,
+                  vocab=32000, chunk=1024, side=64, s_heads=32, s_dim=64, s_state=64, s_groups=4),
+    "1b": dict(width=2048, layers=8, heads=16, kv_heads=4, head_dim=128, window=256, r_heads=16, r_qk=4, r_dim=128,
+               r_vdim=128, f_heads=16, f_dim=128, f_vdim=128, ff=4096, experts=32, top=4, e_ff=512, shared=2048,
+               vocab=32000, chunk=1024, side=64, s_heads=64, s_dim=64, s_state=128, s_groups=8),
+    "8b": dict(width=4096, layers=8, heads=32, kv_heads=8, head_dim=128, window=256, r_heads=32, r_qk=8, r_dim=128,
+               r_vdim=128, f_heads=32, f_dim=128, f_vdim=128, ff=7168, experts=64, top=4, e_ff=1024, shared=3072,
+               vocab=32000, chunk=1024, side=64, s_heads=128, s_dim=64, s_state=128, s_groups=8),
+}
+
+
+def gofezen_config(sz: dict, max_positions: int) -> dict:
+    """Layers in the order forget-gate (dense feed-forward), side-by-side (routed experts), ..."""
+    par = {"type": "parallel",
+           "mlp": {"kind": "moe", "router": {"experts": sz["experts"], "top": sz["top"]}, "expert": {"ff": sz["e_ff"]},
+                   "shared": {"ff": sz["shared"]}},
+           "mixer": {"left": {"conv": 3, "dim": sz["head_dim"], "heads": sz["heads"], "kv_heads": sz["kv_heads"],
+                              "mask": {"size": sz["window"]}, "scale": 1.0 / math.sqrt(sz["head_dim"]), "vdim": sz["head_dim"]},
+                     "left_scale": 0.6,
+                     "right": {"conv": 4, "dim": sz["r_dim"], "heads": sz["r_heads"], "kv_heads": sz["r_qk"], "vdim": sz["r_vdim"]},
+                     "right_scale": 0.9}}
+    fg = {"type": "hgrn2", "mlp": {"kind": "dense", "ff": sz["ff"]},
+          "mixer": {"dim": sz["f_dim"], "heads": sz["f_heads"], "vdim": sz["f_vdim"]}}
+    return {"architecture": "Gofezen", "embedding": {"scale": 8.0}, "layers": [dict((fg, par)[i % 2]) for i in range(sz["layers"])],
+            "logit_scale": 0.5, "logit_softcap": 30.0, "max_positions": max_positions, "norm": {"eps": 1e-6},
+            "vocab": sz["vocab"], "width": sz["width"]}
+
+
+def build_gofezen(sz, batch, max_positions, dev, dtype):
+    from lite_llama_b200.executor import ModelRunner
+    from lite_llama_b200.executor.layered_decoder import map_gofezen_weights, parse_gofezen_config, random_gofezen_tensors
+
+    conf = parse_gofezen_config(gofezen_config(sz, max_positions))
+    conf.validate()
+    weights = map_gofezen_weights(conf, random_gofezen_tensors(conf, seed=0), dev, dtype)
+    return ModelRunner(conf, weights, batch * max_positions, device=dev, dtype=dtype, max_requests=batch)
+
+
+def gofezen_step_throughput(sz, batch, prompt, dev, dtype, flush) -> dict:
+    """tokens/s of a whole-prompt step and of a decode step: Gofezen beside the Tisosun model (the other design of
+    parallel blocks with recurrent layers and attention side by side with linear attention) of the same width, depth,
+    attention geometry and dense feed-forward width."""
+    max_pos = prompt + 64
+    out = {}
+    gen = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, sz["vocab"], (batch, prompt), generator=gen)
+    tok = [[int(t)] for t in torch.randint(0, sz["vocab"], (batch,), generator=gen)]
+    for name, build in (("gofezen", lambda: build_gofezen(sz, batch, max_pos, dev, dtype)),
+                        ("tisosun", lambda: build_tisosun(sz, batch, max_pos, dev, dtype))):
+        r = build()
+        r.enable_ragged_decode_graphs(widths=(batch,), ctx_buckets=(max_pos,))
+        reqs = []
+
+        def prefill():
+            for q in reqs:
+                r.close_request(q)
+            reqs[:] = [r.open_request() for _ in range(batch)]
+            return r.forward_ragged([(q, ids[i].tolist()) for i, q in enumerate(reqs)])
+
+        pre = timed(prefill, flush, warmup=2, reps=3)
+        state = {"n": 0}
+
+        def decode():
+            if state["n"] >= 48:
+                prefill()
+                state["n"] = 0
+            state["n"] += 1
+            return r.forward_ragged([(q, tok[i]) for i, q in enumerate(reqs)])
+
+        dec = timed(decode, flush, warmup=3, reps=9)
+        out[name] = {"prefill_ms": pre, "prefill_tok_s": batch * prompt / pre * 1e3, "decode_ms": dec,
+                     "decode_tok_s": batch / dec * 1e3, "weight_bytes_per_step": r.model.w.nbytes_per_step()}
+        del r, reqs, prefill, decode
+        gc.collect()
+        torch.cuda.empty_cache()
+    return out
+
+
+def gofezen_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) -> list[dict]:
+    """Every kernel of the Gofezen path alone at the size's shapes beside its like kernel of the Tisosun path (the
+    closest existing model; for the routed experts the ungated grouped experts of the Pesivik path), with the fraction
+    of the measured roofline each reaches."""
+    import lite_llama_b200.kernels as K
+    from lite_llama_b200.executor.layered_decoder import split_plan
+
+    es = 2
+    W, H, G, D, ff, win = sz["width"], sz["heads"], sz["kv_heads"], sz["head_dim"], sz["ff"], sz["window"]
+    RH, RQ, RD, RV = sz["r_heads"], sz["r_qk"], sz["r_dim"], sz["r_vdim"]
+    FH, FD, FV = sz["f_heads"], sz["f_dim"], sz["f_vdim"]
+    E, top, eff = sz["experts"], sz["top"], sz["e_ff"]
+    T, ctx = batch * prompt, prompt
+    rows: list[dict] = []
+
+    def i32(v):
+        return torch.tensor(list(v), dtype=torch.int32, device=dev)
+
+    def rnd(*shape, dt=dtype, s=1.0):
+        return (torch.randn(*shape, device=dev) * s).to(dt)
+
+    def add(name, like, fn, nbytes=0, flops=0, like_fn=None, like_bytes=None, like_flops=None):
+        ms = timed(fn, flush)
+        row = {"kernel": name, "us": ms * 1e3}
+        if flops:
+            row.update(tflops=flops / ms / 1e9, frac=flops / ms / 1e9 / tflops, bound="tensor")
+        else:
+            row.update(gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / hbm_gbs, bound="hbm")
+        if like_fn is not None:
+            lms = timed(like_fn, flush)
+            lf = like_flops if like_flops is not None else flops
+            lb = like_bytes if like_bytes is not None else nbytes
+            lfrac = lf / lms / 1e9 / tflops if flops else lb / lms / 1e6 / hbm_gbs
+            row.update(like=like, like_us=lms * 1e3, like_frac=lfrac,
+                       distance_ratio=(lfrac / row["frac"]) if row["frac"] else None)
+        rows.append(row)
+
+    p_start, p_ctx, p_slot = i32(range(0, T + 1, prompt)), i32([0] * batch), i32(range(batch))
+    d_start, d_ctx = i32(range(batch + 1)), i32([ctx] * batch)
+    # ---------------- residual stream: scaled branches + feed-forward + the next layer's input norm in one pass
+    resid = torch.randn(T, W, device=dev)
+    a, b, c, w1, w2 = rnd(T, W), rnd(T, W), rnd(T, W), rnd(W, s=0.1) + 1, rnd(W, s=0.1) + 1
+    add("branch_sum_residual (two scaled branches + feed-forward + next input norm)",
+        "branch_sum_residual (two normed branches + feed-forward)",
+        lambda: K.branch_sum_residual(resid, a, None, b, None, c, 1e-6, 0.6, want_act=False, scale_b=0.9, next_weight=w1),
+        nbytes=T * W * (4 + 4 + 3 * es + es),
+        like_fn=lambda: K.branch_sum_residual(resid, a, w1, b, w2, c, 1e-6, 0.5), like_bytes=T * W * (4 + 4 + 3 * es + es))
+    lg = rnd(batch, sz["vocab"])
+    add("softcap_to_f32 (scaled, capped logits of a decode step)", None, lambda: K.softcap_to_f32(lg, 30.0, 0.5),
+        nbytes=batch * sz["vocab"] * (es + 4))
+    # ---------------- attention half: convolution, unit-RMS + cache write, window attention over wide values, head mix
+    ch = H * D + 2 * G * D
+    proj = rnd(T, ch, s=0.5)
+    cw, cb = rnd(ch, 3, s=0.5), torch.zeros(ch, dtype=dtype, device=dev)
+    tail = torch.zeros(batch, 2, ch, dtype=dtype, device=dev)
+    SH, SP, SN, SG = sz["s_heads"], sz["s_dim"], sz["s_state"], sz["s_groups"]
+    lproj, lw, lb = rnd(T, 2 * W), rnd(W, 4, s=0.5), rnd(W, s=0.1)
+    ltail = torch.zeros(batch, 3, W, dtype=dtype, device=dev)
+    add("causal convolution of q | k | v (prompts, 3 taps, no activation)", "causal convolution without activation (gated LRU)",
+        lambda: K.causal_conv_silu(proj, 0, ch, cw, cb, tail, p_start, p_ctx, p_slot, activation=False), nbytes=T * ch * 2 * es,
+        like_fn=lambda: K.causal_conv_silu(lproj, W, W, lw, lb, ltail, p_start, p_ctx, p_slot, activation=False),
+        like_bytes=T * W * 2 * es)
+    kvw = G * 2 * D
+    pool = rnd(batch * (ctx + 1), kvw, s=0.5)
+    tab = torch.arange(batch * (ctx + 1), dtype=torch.int32, device=dev).view(batch, ctx + 1)
+    rows_p = tab[:, :ctx].reshape(-1).contiguous()
+    pos_p = i32(list(range(prompt)) * batch)
+    ones = torch.ones(D, dtype=dtype, device=dev)
+    rot = D // 2
+    f, mag = K.rotary_frequencies(rot, 10000.0, 8.0, 4096.0, 32.0, 1.0)
+    cs = K.rope_table_freqs(pos_p, torch.tensor(f, dtype=torch.float64, device=dev), mag)
+    prep_bytes = T * ((2 * H + 2 * G) * D * es + 2 * G * D * es)
+    add("head_norm_rope_prepare (unit-RMS of q and k, no rotation, cache write)", "head_norm_rope_prepare (weights, rotation)",
+        lambda: K.head_norm_rope_prepare(proj, pool, rows_p, None, ones, ones, H, G, D, D, 0, 1e-6), nbytes=prep_bytes,
+        like_fn=lambda: K.head_norm_rope_prepare(proj, pool, rows_p, cs, ones, ones, H, G, D, D, rot, 1e-6),
+        like_bytes=prep_bytes + T * rot * 4)
+    per_call = max(c for c in range(1, G + 1) if G % c == 0 and (c * D <= 128 or c == 1))
+    calls, width = G // per_call, per_call * D
+    wide = torch.empty(T, calls * H * width, dtype=dtype, device=dev)
+    out = torch.empty(T, H * D, dtype=dtype, device=dev)
+    scale = 1.0 / math.sqrt(D)
+    seen = sum(min(t + 1, win) for t in range(prompt))
+    chunk = sz["chunk"]
+    like_seen = sum(t % chunk + 1 for t in range(prompt))
+
+    def mixed_prompt():
+        for cidx in range(calls):
+            K.sink_attention(wide[:, cidx * H * width:(cidx + 1) * H * width], proj, pool, tab, p_start, p_ctx, p_slot, None,
+                             batch, prompt, None, H, G, D, width, scale, 0.0, window=win, v_col0=G * D + cidx * width,
+                             v_head_stride=0)
+
+    add("window attention, every value head under every query head's weights (prompts, window %d, %d calls)" % (win, calls),
+        "block-masked attention (prompts, blocks of %d)" % chunk, mixed_prompt,
+        flops=batch * H * seen * (2 * D + 2 * G * D),
+        like_fn=lambda: K.sink_attention(out, proj, pool, tab, p_start, p_ctx, p_slot, None, batch, prompt, None, H, G, D, D,
+                                         scale, 30.0, block=chunk),
+        like_flops=4 * batch * H * D * like_seen)
+    talk = rnd(H, H, s=0.2)
+    add("head_mix (weights mixed across heads, on the outputs)", None,
+        lambda: K.head_mix(wide, talk, H, G, per_call, D), nbytes=T * H * D * (G + 1) * es)
+    keys = min(ctx + 1, win)
+    splits, per = split_plan(keys)
+
+    def mixed_decode():
+        for cidx in range(calls):
+            K.sink_attention(wide[:batch, cidx * H * width:(cidx + 1) * H * width], proj, pool, tab, d_start, d_ctx, p_slot, None,
+                             batch, 1, None, H, G, D, width, scale, 0.0, num_splits=splits, split_keys=per, window=win,
+                             v_col0=G * D + cidx * width, v_head_stride=0)
+
+    lkeys = min(ctx + 1, ctx % chunk + 1)
+    lsplits, lper = split_plan(min(ctx + 1, chunk))
+    add("window attention over wide values (decode, %d of %d keys seen, %d calls)" % (keys, ctx + 1, calls),
+        "block-masked attention (decode, %d keys seen)" % lkeys, mixed_decode, nbytes=batch * keys * kvw * es,
+        like_fn=lambda: K.sink_attention(out, proj, pool, tab, d_start, d_ctx, p_slot, None, batch, 1, None, H, G, D, D, scale,
+                                         30.0, num_splits=lsplits, split_keys=lper, block=chunk),
+        like_bytes=batch * lkeys * kvw * es)
+    # ---------------- the two memories beside Tisosun's linear attention (token scan and tensor-core chunks)
+    rin = RH * RV
+    tproj = rnd(T, 2 * rin + 2 * RH * RD, s=0.5)
+    dec = torch.tensor([1.0 - 2.0 ** (-2 - 6 * h / RH) for h in range(RH)], dtype=torch.float32, device=dev)
+    tst = torch.zeros(batch, RH, RD, RV, device=dev)
+    tx = tproj[:, :rin + 2 * RH * RD]
+    like_scan = lambda: K.ssm_scan(tx, None, None, None, None, tst, p_start, p_ctx, p_slot, RH, RH, RD, RV, fixed_decay=dec, silu_inputs=True)
+    like_chunk = lambda: K.decay_attention(tx, tst, dec, p_start, p_ctx, p_slot, RH, RD, RV, prompt)
+    like_dec = lambda: K.ssm_scan(tx[:batch], None, None, None, None, tst, d_start, d_ctx, p_slot, RH, RH, RD, RV, fixed_decay=dec, silu_inputs=True)
+    like_bytes = T * ((rin + 2 * RH * RD) * es + rin * 4) + batch * RH * RD * RV * 4
+    dch = 2 * RQ * RD + RH * RV
+    dproj = rnd(T, dch + 2 * RH, s=0.5)
+    dst = torch.zeros(batch, RH, RD, RV, device=dev)
+    dtb, alog = rnd(RH) - 1, rnd(RH, s=0.5) - 1
+    dq, dk, dv = dproj[:, :RQ * RD], dproj[:, RQ * RD:2 * RQ * RD], dproj[:, 2 * RQ * RD:dch]
+    p0, p1 = dproj[:, dch:dch + RH], dproj[:, dch + RH:]
+
+    def delta(n, start, cx):
+        return K.gated_linear_scan("delta_rule", dst, dq[:n], dk[:n], dv[:n], start, cx, p_slot, RH, RQ, RD, RV, c0=dtb, c1=alog,
+                                   p0=p0[:n], p1=p1[:n], q_scale=RD ** -0.5)
+
+    d_bytes = T * ((dch + 2 * RH) * es + rin * 4) + batch * RH * RD * RV * 4
+    add("gated_linear_scan, delta rule (prompts)", "ssm_scan, fixed decay (prompts, token by token)",
+        lambda: delta(T, p_start, p_ctx), nbytes=d_bytes, like_fn=like_scan, like_bytes=like_bytes)
+    rows.append(dict(rows[-1], like="decay_attention (prompts, 64-token chunks on the tensor cores)"))
+    lms = timed(like_chunk, flush)
+    rows[-1].update(like_us=lms * 1e3, like_frac=like_bytes / lms / 1e6 / hbm_gbs,
+                    distance_ratio=like_bytes / lms / 1e6 / hbm_gbs / rows[-1]["frac"])
+    add("gated_linear_scan, delta rule (decode)", "ssm_scan, fixed decay (decode)", lambda: delta(batch, d_start, d_ctx),
+        nbytes=batch * RH * RD * RV * 8, like_fn=like_dec, like_bytes=batch * RH * RD * RV * 8)
+    fproj = rnd(T, 2 * FH * FD + FH * FV, s=0.5)
+    fst = torch.zeros(batch, FH, FD, FV, device=dev)
+    low = torch.rand(FH * FD, device=dev).to(dtype) * 0.9
+    fq, fk, fv = fproj[:, :FH * FD], fproj[:, FH * FD:2 * FH * FD], fproj[:, 2 * FH * FD:]
+
+    def forget(n, start, cx):
+        return K.gated_linear_scan("forget_gate", fst, fq[:n], fk[:n], fv[:n], start, cx, p_slot, FH, FH, FD, FV, c0=low)
+
+    f_bytes = T * ((2 * FH * FD + FH * FV) * es + FH * FV * 4) + batch * FH * FD * FV * 4
+    add("gated_linear_scan, forget gate (prompts)", "ssm_scan, fixed decay (prompts, token by token)",
+        lambda: forget(T, p_start, p_ctx), nbytes=f_bytes, like_fn=like_scan, like_bytes=like_bytes)
+    add("gated_linear_scan, forget gate (decode)", "ssm_scan, fixed decay (decode)", lambda: forget(batch, d_start, d_ctx),
+        nbytes=batch * FH * FD * FV * 8, like_fn=like_dec, like_bytes=batch * RH * RD * RV * 8)
+    yf = torch.randn(T, rin, device=dev)
+    nw, nv = rnd(rin, s=0.1) + 1, rnd(RV, s=0.1) + 1
+    gate = rnd(T, rin)
+    add("head_norm_gate (per-head norm, SiLU gate)", "norm_sigmoid_gate", lambda: K.head_norm_gate(yf, nv, RH, 1e-6, gate),
+        nbytes=T * rin * (4 + es + es), like_fn=lambda: K.norm_sigmoid_gate(yf, gate, nw, 1e-6))
+    rcw, rcb = rnd(dch, 4, s=0.5), torch.zeros(dch, dtype=dtype, device=dev)
+    rtail = torch.zeros(batch, 3, dch, dtype=dtype, device=dev)
+    add("causal convolution + SiLU of q' | k' | v' (prompts, 4 taps)", "causal convolution without activation (gated LRU)",
+        lambda: K.causal_conv_silu(dproj, 0, dch, rcw, rcb, rtail, p_start, p_ctx, p_slot), nbytes=T * dch * 2 * es,
+        like_fn=lambda: K.causal_conv_silu(lproj, W, W, lw, lb, ltail, p_start, p_ctx, p_slot, activation=False),
+        like_bytes=T * W * 2 * es)
+    # ---------------- feed-forwards
+    gu = rnd(T, 2 * ff)
+    zrow = rnd(T, 8)
+    add("swiglu_scaled (shared expert: SiLU * up * logistic token gate)", "swiglu_forward",
+        lambda: K.swiglu_scaled(gu[:, :ff], gu[:, ff:], None, zrow[:, :1]), nbytes=T * ff * 3 * es,
+        like_fn=lambda: K.swiglu_forward(gu[:, :ff], gu[:, ff:]))
+    x = rnd(T, W, s=0.5)
+    router = rnd(E, W, s=W ** -0.5)
+    add("route_sigmoid_groups (scores kept as they are)", "route_sigmoid_groups (renormalised)",
+        lambda: K.route_sigmoid_groups(x, router, None, top, 1, 1, renormalize=False), flops=2 * T * E * W,
+        like_fn=lambda: K.route_sigmoid_groups(x, router, None, top, 1, 1))
+    wts, ids = K.route_sigmoid_groups(x, router, None, top, 1, 1, renormalize=False)
+    wgu, wdn = rnd(E, 2 * eff, W, s=W ** -0.5), rnd(E, W, eff, s=eff ** -0.5)
+    wup = rnd(E, 2 * eff, W, s=W ** -0.5)                            # ungated experts of equal weight bytes and FLOPs
+    wdn2 = rnd(E, W, 2 * eff, s=eff ** -0.5)
+    add("grouped_experts, gated, weight on the input (prompts)", "grouped_experts, ungated GELU (equal first product)",
+        lambda: K.grouped_experts(x, wgu, wdn, wts, ids, activation="silu", gated=True, weight_on_input=True),
+        flops=2 * T * top * 3 * eff * W, like_fn=lambda: K.grouped_experts(x, wup, wdn2, wts, ids),
+        like_flops=2 * T * top * 4 * eff * W)
+    xd, wd, idd = x[:batch], wts[:batch].contiguous(), ids[:batch].contiguous()
+    add("grouped_experts, gated, weight on the input (decode)", "grouped_experts, ungated GELU (equal first product)",
+        lambda: K.grouped_experts(xd, wgu, wdn, wd, idd, activation="silu", gated=True, weight_on_input=True),
+        nbytes=min(E, batch * top) * 3 * eff * W * es, like_fn=lambda: K.grouped_experts(xd, wup, wdn2, wd, idd),
+        like_bytes=min(E, batch * top) * 4 * eff * W * es)
+    return rows
+
+
 def run(args) -> None:
     from bench import ClockSampler, peaks
 
@@ -791,7 +1073,8 @@ def run(args) -> None:
     flush = _flush_buffer(dev)
     sizes = [s for s in (args.design_sizes or "small,1b,8b").split(",") if s]
     table, steps, kernels = {"pesivik": (P_SIZES, pesivik_step_throughput, pesivik_kernel_table),
-                             "tisosun": (T_SIZES, tisosun_step_throughput, tisosun_kernel_table)}.get(
+                             "tisosun": (T_SIZES, tisosun_step_throughput, tisosun_kernel_table),
+                             "gofezen": (G_SIZES, gofezen_step_throughput, gofezen_kernel_table)}.get(
         args.design, (SIZES, step_throughput, kernel_table))
     result = {"design": args.design, "dtype": "bf16", "data": "synthetic ids, random weights", "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": tflops, "source": src},
               "batch": args.batch, "prompt_len": args.prompt_len, "l2_policy": "256 MiB written between timed runs", "sizes": {}}
