@@ -9,11 +9,11 @@
 //                          S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 //                          (the read-out sees the current token's write)
 //
-// Thread = one value column of one head: its D memory entries live in registers, so the two contractions over D of a
-// token (S^T k, S^T q) are sums inside a thread and the serial chain of a token has no cross-thread step.  A CTA =
-// (block of value columns, head, sequence) stages 16 tokens at a time: the token's gates, unit norms and scalars are
-// evaluated in fp32 by the warps in parallel and left in shared memory, every thread fetches its own column of v for
-// the 16 tokens, then the 16 updates run back to back.  A sequence without cached tokens starts from zero and never
+// Four neighbouring lanes share one value column of one head and hold a quarter of its D memory entries each in
+// registers, so the two contractions over D of a token (S^T k, S^T q) are sums inside a thread plus two shuffles.  A
+// CTA = (64 value columns, head, sequence) stages 16 tokens at a time: the token's gates, unit norms and scalars are
+// evaluated in fp32 by the warps in parallel and left in shared memory with the chunk's v columns, then the 16
+// updates run back to back.  A sequence without cached tokens starts from zero and never
 // reads its slot; every sequence writes its slot at the end of the step.
 //
 //   head_norm_gate   out[t, h, :] = unit_rms(y[t, h, :]) * w * (silu(gate[t, h, :]) or 1): the per-head output norm
@@ -25,6 +25,7 @@
 //                    a per-row fp32 factor (an expert weight on the expert's input: W (s x) = s (W x)) and whose output
 //                    a per-row logistic gate (both optional)
 #include "common.cuh"
+#include "rowvec.cuh"
 
 namespace {
 
@@ -48,24 +49,38 @@ struct GlaArgs {
   float q_scale, unit_eps;
 };
 
+constexpr int kParts = 4;                 // threads that share one value column (neighbouring lanes), each with DP / 4 rows
+constexpr int kScanThreads = 256;
+
 template <typename T, int DP, int MODE>
-__global__ void __launch_bounds__(128) gated_linear_scan_kernel(GlaArgs a) {
+__global__ void __launch_bounds__(kScanThreads) gated_linear_scan_kernel(GlaArgs a) {
   pdl_prologue();
+  constexpr int R4 = DP / 16;                       // float4 groups of memory rows per thread
+  constexpr int COLS = kScanThreads / kParts;
   __shared__ __align__(16) float qs[kTok * DP];
   __shared__ __align__(16) float ks[kTok * DP];     // mode 1: unit keys; mode 0: forget gates
+  __shared__ float vs[kTok * COLS];
   __shared__ float sc[kTok * 2];                    // mode 1: (g, beta) per token
   const int D = a.D, V = a.V, H = a.H;
   const int h = blockIdx.y, s = blockIdx.z;
   const int qh = h / (H / a.QH);
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  const int part = threadIdx.x & (kParts - 1), lcol = threadIdx.x / kParts;
+  const int col = blockIdx.x * COLS + lcol;
   const bool live = col < V;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int start = a.seq_start[s], len = a.seq_start[s + 1] - start, ctx = a.seq_ctx[s];
   const int64_t slot = a.seq_slot[s];
   float* sp = a.state + ((slot * H + h) * (int64_t)D) * V;
-  float S[DP];
+  // thread (col, part) holds rows d = 16 i + 4 part + e (i < R4, e < 4): the four parts of a column read four
+  // neighbouring float4 of a staged vector, so a warp's reads fall in different banks
+  float S[R4 * 4];
 #pragma unroll
-  for (int d = 0; d < DP; ++d) S[d] = (ctx > 0 && live && d < D) ? sp[(int64_t)d * V + col] : 0.f;
+  for (int i = 0; i < R4; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int d = 16 * i + 4 * part + e;
+      S[4 * i + e] = (ctx > 0 && live && d < D) ? sp[(int64_t)d * V + col] : 0.f;
+    }
   const T* qp = (const T*)a.q;
   const T* kp = (const T*)a.k;
   const T* vp = (const T*)a.v;
@@ -77,9 +92,9 @@ __global__ void __launch_bounds__(128) gated_linear_scan_kernel(GlaArgs a) {
     for (int t = warp; t < nt; t += nw) {
       const int64_t row = start + t0 + t;
       if (MODE == 1) {
-        float qv[DP / 32], kv[DP / 32], sq = 0.f, sk = 0.f;
+        float qv[(DP + 31) / 32], kv[(DP + 31) / 32], sq = 0.f, sk = 0.f;
 #pragma unroll
-        for (int i = 0; i < DP / 32; ++i) {
+        for (int i = 0; i < (DP + 31) / 32; ++i) {
           const int d = lane + 32 * i;
           qv[i] = d < D ? to_f32(qp[row * a.q_stride + qh * D + d]) : 0.f;
           kv[i] = d < D ? to_f32(kp[row * a.k_stride + qh * D + d]) : 0.f;
@@ -89,9 +104,9 @@ __global__ void __launch_bounds__(128) gated_linear_scan_kernel(GlaArgs a) {
         const float rq = a.q_scale / sqrtf(warp_reduce_sum(sq) + a.unit_eps);
         const float rk = 1.0f / sqrtf(warp_reduce_sum(sk) + a.unit_eps);
 #pragma unroll
-        for (int i = 0; i < DP / 32; ++i) {
-          qs[t * DP + lane + 32 * i] = qv[i] * rq;
-          ks[t * DP + lane + 32 * i] = kv[i] * rk;
+        for (int i = 0; i < (DP + 31) / 32; ++i) {
+          const int d = lane + 32 * i;
+          if (d < DP) { qs[t * DP + d] = qv[i] * rq; ks[t * DP + d] = kv[i] * rk; }
         }
         if (lane == 0) {
           const float dt = gla_softplus(to_f32(((const T*)a.p1)[row * a.p1_stride + h]) + dtb);
@@ -100,7 +115,7 @@ __global__ void __launch_bounds__(128) gated_linear_scan_kernel(GlaArgs a) {
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < DP / 32; ++i) {
+        for (int i = 0; i < (DP + 31) / 32; ++i) {
           const int d = lane + 32 * i;
           float qv = 0.f, f = 1.f;                   // rows beyond D: nothing written, nothing read
           if (d < D) {
@@ -108,71 +123,104 @@ __global__ void __launch_bounds__(128) gated_linear_scan_kernel(GlaArgs a) {
             const float lo = to_f32(((const T*)a.c0)[h * D + d]);
             f = lo + (1.0f - lo) * gla_sigmoid(to_f32(kp[row * a.k_stride + h * D + d]));
           }
-          qs[t * DP + d] = qv;
-          ks[t * DP + d] = f;
+          if (d < DP) { qs[t * DP + d] = qv; ks[t * DP + d] = f; }
         }
       }
     }
-    float vr[kTok];
-#pragma unroll
-    for (int t = 0; t < kTok; ++t)
-      vr[t] = (t < nt && live) ? to_f32(vp[(int64_t)(start + t0 + t) * a.v_stride + h * V + col]) : 0.f;
+    for (int i = threadIdx.x; i < nt * COLS; i += kScanThreads) {
+      const int t = i / COLS, c = blockIdx.x * COLS + (i - t * COLS);
+      vs[i] = c < V ? to_f32(vp[(int64_t)(start + t0 + t) * a.v_stride + h * V + c]) : 0.f;
+    }
     __syncthreads();
-#pragma unroll
-    for (int t = 0; t < kTok; ++t) {
-      if (t >= nt) break;
-      const float4* q4 = reinterpret_cast<const float4*>(qs + t * DP);
-      const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP);
+#pragma unroll 2
+    for (int t = 0; t < nt; ++t) {
+      const float4* q4 = reinterpret_cast<const float4*>(qs + t * DP) + part;
+      const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP) + part;
+      const float x = vs[t * COLS + lcol];
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
       if (MODE == 1) {
         const float g = sc[2 * t], beta = sc[2 * t + 1];
+        float4 kk[R4];
         float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < DP / 4; ++i) {
-          const float4 kk = k4[i];
-          d0 = fmaf(S[4 * i], kk.x, d0); d1 = fmaf(S[4 * i + 1], kk.y, d1);
-          d2 = fmaf(S[4 * i + 2], kk.z, d2); d3 = fmaf(S[4 * i + 3], kk.w, d3);
+        for (int i = 0; i < R4; ++i) {
+          kk[i] = k4[4 * i];
+          d0 = fmaf(S[4 * i], kk[i].x, d0); d1 = fmaf(S[4 * i + 1], kk[i].y, d1);
+          d2 = fmaf(S[4 * i + 2], kk[i].z, d2); d3 = fmaf(S[4 * i + 3], kk[i].w, d3);
         }
-        const float u = beta * (vr[t] - g * ((d0 + d1) + (d2 + d3)));
+        float dot = (d0 + d1) + (d2 + d3);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        const float u = beta * (x - g * dot);
 #pragma unroll
-        for (int i = 0; i < DP / 4; ++i) {
-          const float4 kk = k4[i], qq = q4[i];
-          S[4 * i] = fmaf(g, S[4 * i], kk.x * u); S[4 * i + 1] = fmaf(g, S[4 * i + 1], kk.y * u);
-          S[4 * i + 2] = fmaf(g, S[4 * i + 2], kk.z * u); S[4 * i + 3] = fmaf(g, S[4 * i + 3], kk.w * u);
+        for (int i = 0; i < R4; ++i) {
+          const float4 qq = q4[4 * i];
+          S[4 * i] = fmaf(g, S[4 * i], kk[i].x * u); S[4 * i + 1] = fmaf(g, S[4 * i + 1], kk[i].y * u);
+          S[4 * i + 2] = fmaf(g, S[4 * i + 2], kk[i].z * u); S[4 * i + 3] = fmaf(g, S[4 * i + 3], kk[i].w * u);
           o0 = fmaf(S[4 * i], qq.x, o0); o1 = fmaf(S[4 * i + 1], qq.y, o1);
           o2 = fmaf(S[4 * i + 2], qq.z, o2); o3 = fmaf(S[4 * i + 3], qq.w, o3);
         }
       } else {
-        const float x = vr[t];
 #pragma unroll
-        for (int i = 0; i < DP / 4; ++i) {
-          const float4 ff = k4[i], qq = q4[i];
+        for (int i = 0; i < R4; ++i) {
+          const float4 ff = k4[4 * i], qq = q4[4 * i];
           S[4 * i] = fmaf(ff.x, S[4 * i], (1.0f - ff.x) * x); S[4 * i + 1] = fmaf(ff.y, S[4 * i + 1], (1.0f - ff.y) * x);
           S[4 * i + 2] = fmaf(ff.z, S[4 * i + 2], (1.0f - ff.z) * x); S[4 * i + 3] = fmaf(ff.w, S[4 * i + 3], (1.0f - ff.w) * x);
           o0 = fmaf(S[4 * i], qq.x, o0); o1 = fmaf(S[4 * i + 1], qq.y, o1);
           o2 = fmaf(S[4 * i + 2], qq.z, o2); o3 = fmaf(S[4 * i + 3], qq.w, o3);
         }
       }
-      if (live) a.y[(int64_t)(start + t0 + t) * H * V + h * V + col] = (o0 + o1) + (o2 + o3);
+      float o = (o0 + o1) + (o2 + o3);
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (live && part == 0) a.y[(int64_t)(start + t0 + t) * H * V + h * V + col] = o;
     }
   }
   if (live) {
 #pragma unroll
-    for (int d = 0; d < DP; ++d)
-      if (d < D) sp[(int64_t)d * V + col] = S[d];
+    for (int i = 0; i < R4; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int d = 16 * i + 4 * part + e;
+        if (d < D) sp[(int64_t)d * V + col] = S[4 * i + e];
+      }
   }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(128) head_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ y,
                                                              const T* __restrict__ gate, int64_t gs,
-                                                             const T* __restrict__ w, int heads, int V, float eps) {
+                                                             const T* __restrict__ w, int heads, int V, float eps,
+                                                             int vec) {
   pdl_prologue();
   const int64_t t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int h = warp; h < heads; h += nw) {
     const float* yr = y + (t * heads + h) * (int64_t)V;
     float ss = 0.f;
+    if (vec) {                                       // 4 elements per access
+      for (int i = lane * 4; i < V; i += 128) {
+        float v[4];
+        row_load4(yr + i, v);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) ss = fmaf(v[c], v[c], ss);
+      }
+      const float rstd = 1.0f / sqrtf(warp_reduce_sum(ss) / (float)V + eps);
+      for (int i = lane * 4; i < V; i += 128) {
+        float v[4], g[4];
+        row_load4(yr + i, v);
+        row_load4(w + i, g);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) v[c] = v[c] * rstd * g[c];
+        if (gate) {
+          row_load4(gate + t * gs + (int64_t)h * V + i, g);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) v[c] *= gla_silu(g[c]);
+        }
+        row_store4(out + (t * heads + h) * (int64_t)V + i, v);
+      }
+      continue;
+    }
     for (int i = lane; i < V; i += 32) { const float v = yr[i]; ss = fmaf(v, v, ss); }
     const float rstd = 1.0f / sqrtf(warp_reduce_sum(ss) / (float)V + eps);
     for (int i = lane; i < V; i += 32) {
@@ -202,6 +250,50 @@ __global__ void head_mix_kernel(T* __restrict__ out, const T* __restrict__ wide,
   }
 }
 
+// the same with 4 value columns per thread (vdim and the row stride multiples of 4, aligned pointers)
+template <typename T>
+__global__ void head_mix_vec_kernel(T* __restrict__ out, const T* __restrict__ wide, int64_t wide_stride,
+                                    const T* __restrict__ mix, int heads, int kv_heads, int per_call, int Dv,
+                                    int64_t total4) {
+  pdl_prologue();
+  const int per = heads / kv_heads, q4 = Dv / 4;
+  const int64_t call_stride = (int64_t)heads * per_call * Dv;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total4; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % q4) * 4;
+    const int h = (int)((idx / q4) % heads);
+    const int64_t t = idx / ((int64_t)q4 * heads);
+    const int c = h / per;
+    const T* src = wide + t * wide_stride + (c / per_call) * call_stride + (int64_t)(c % per_call) * Dv + i;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int g = 0; g < heads; ++g) {
+      float v[4];
+      row_load4(src + (int64_t)g * per_call * Dv, v);
+      const float m = to_f32(mix[h * heads + g]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[e] = fmaf(m, v[e], acc[e]);
+    }
+    row_store4(out + (t * heads + h) * (int64_t)Dv + i, acc);
+  }
+}
+
+template <typename T>
+__global__ void swiglu_scaled_vec_kernel(T* __restrict__ out, int64_t os, const T* __restrict__ gate, int64_t gs,
+                                         const T* __restrict__ up, int64_t us, const float* __restrict__ in_scale,
+                                         const T* __restrict__ z, int64_t zs, int64_t n4, int64_t total4) {
+  pdl_prologue();
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total4; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / n4, i = (idx - r * n4) * 4;
+    const float s = in_scale ? in_scale[r] : 1.0f;
+    const float zo = z ? gla_sigmoid(to_f32(z[r * zs])) : 1.0f;
+    float g[4], u[4];
+    row_load4(gate + r * gs + i, g);
+    row_load4(up + r * us + i, u);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) g[e] = gla_silu(s * g[e]) * (s * u[e]) * zo;
+    row_store4(out + r * os + i, g);
+  }
+}
+
 template <typename T>
 __global__ void swiglu_scaled_kernel(T* __restrict__ out, int64_t os, const T* __restrict__ gate, int64_t gs,
                                      const T* __restrict__ up, int64_t us, const float* __restrict__ in_scale,
@@ -211,18 +303,18 @@ __global__ void swiglu_scaled_kernel(T* __restrict__ out, int64_t os, const T* _
     const int64_t r = idx / n, i = idx - r * n;
     const float s = in_scale ? in_scale[r] : 1.0f;
     const float g = s * to_f32(gate[r * gs + i]), u = s * to_f32(up[r * us + i]);
-    float v = gla_silu(g) * u;
-    if (z) v *= gla_sigmoid(to_f32(z[r * zs]));
-    out[r * os + i] = from_f32<T>(v);
+    const float zo = z ? gla_sigmoid(to_f32(z[r * zs])) : 1.0f;
+    out[r * os + i] = from_f32<T>(gla_silu(g) * u * zo);
   }
 }
 
 template <typename T, int MODE>
 int launch_scan(const GlaArgs& a, int64_t num_seqs, cudaStream_t st) {
-  const int threads = a.V >= 128 ? 128 : ((a.V + 31) / 32) * 32;
-  const dim3 grid((unsigned)((a.V + threads - 1) / threads), (unsigned)a.H, (unsigned)num_seqs);
-#define B2L_GLA(DPV) b2l_launch(gated_linear_scan_kernel<T, DPV, MODE>, grid, dim3(threads), (size_t)0, st, a)
-  if (a.D <= 32) B2L_GLA(32);
+  constexpr int cols = kScanThreads / kParts;
+  const dim3 grid((unsigned)((a.V + cols - 1) / cols), (unsigned)a.H, (unsigned)num_seqs);
+#define B2L_GLA(DPV) b2l_launch(gated_linear_scan_kernel<T, DPV, MODE>, grid, dim3(kScanThreads), (size_t)0, st, a)
+  if (a.D <= 16) B2L_GLA(16);
+  else if (a.D <= 32) B2L_GLA(32);
   else if (a.D <= 64) B2L_GLA(64);
   else if (a.D <= 128) B2L_GLA(128);
   else B2L_GLA(256);
@@ -273,7 +365,9 @@ extern "C" int b2l_head_norm_gate(void* out, const void* y_f32, const void* gate
   const int threads = heads >= 4 ? 128 : heads * 32;
   B2L_DISPATCH_FLOAT(dtype, "head_norm_gate", {
     b2l_launch(head_norm_gate_kernel<T>, dim3((unsigned)rows), dim3(threads), (size_t)0, st, (T*)out, (const float*)y_f32,
-               (const T*)gate, gate_row_stride, (const T*)weight, heads, vdim, eps);
+               (const T*)gate, gate_row_stride, (const T*)weight, heads, vdim, eps,
+               (int)(vdim % 4 == 0 && gate_row_stride % 4 == 0 && row_aligned4<T>(out) && row_aligned4<T>(gate) &&
+                     row_aligned4<T>(weight) && (uintptr_t)y_f32 % 16 == 0));
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;
@@ -289,10 +383,16 @@ extern "C" int b2l_head_mix(void* out, const void* wide, int64_t wide_row_stride
   if (rows <= 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t total = rows * heads * vdim;
-  const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
   B2L_DISPATCH_FLOAT(dtype, "head_mix", {
-    b2l_launch(head_mix_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, (const T*)wide, wide_row_stride,
-               (const T*)mix, heads, kv_heads, per_call, vdim, total);
+    if (vdim % 4 == 0 && wide_row_stride % 4 == 0 && row_aligned4<T>(out) && row_aligned4<T>(wide)) {
+      const unsigned grid = (unsigned)(cdiv64(total / 4, 256) < 148 * 16 ? cdiv64(total / 4, 256) : 148 * 16);
+      b2l_launch(head_mix_vec_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, (const T*)wide, wide_row_stride,
+                 (const T*)mix, heads, kv_heads, per_call, vdim, total / 4);
+    } else {
+      const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
+      b2l_launch(head_mix_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, (const T*)wide, wide_row_stride,
+                 (const T*)mix, heads, kv_heads, per_call, vdim, total);
+    }
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;
@@ -306,11 +406,19 @@ extern "C" int b2l_swiglu_scaled(void* out, int64_t out_row_stride, const void* 
   if (rows <= 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t total = rows * n;
-  const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
   B2L_DISPATCH_FLOAT(dtype, "swiglu_scaled", {
-    b2l_launch(swiglu_scaled_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, out_row_stride, (const T*)gate,
-               gate_row_stride, (const T*)up, up_row_stride, (const float*)in_scale_f32, (const T*)z, z_row_stride, n,
-               total);
+    if (n % 4 == 0 && out_row_stride % 4 == 0 && gate_row_stride % 4 == 0 && up_row_stride % 4 == 0 &&
+        row_aligned4<T>(out) && row_aligned4<T>(gate) && row_aligned4<T>(up)) {
+      const unsigned grid = (unsigned)(cdiv64(total / 4, 256) < 148 * 32 ? cdiv64(total / 4, 256) : 148 * 32);
+      b2l_launch(swiglu_scaled_vec_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, out_row_stride,
+                 (const T*)gate, gate_row_stride, (const T*)up, up_row_stride, (const float*)in_scale_f32, (const T*)z,
+                 z_row_stride, n / 4, total / 4);
+    } else {
+      const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
+      b2l_launch(swiglu_scaled_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, out_row_stride, (const T*)gate,
+                 gate_row_stride, (const T*)up, up_row_stride, (const float*)in_scale_f32, (const T*)z, z_row_stride, n,
+                 total);
+    }
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;

@@ -328,11 +328,12 @@ def forget_gate_mixer(li: int, spec: ForgetGateAttentionSpec, w: dict[str, torch
     return linear(head_norm_gate(y, w["norm"], spec.heads, eps), w["o"])
 
 
-def wide_value_heads(spec: ConvWindowAttentionSpec, sixteen_bit: bool) -> int:
+def wide_value_heads(spec: ConvWindowAttentionSpec, tensor_tiles: bool) -> int:
     """How many kv heads' values one attention call reads side by side as one wide value head when the softmax
     weights are mixed across heads: the most that divide ``kv_heads`` and stay inside the kernels' value width (128
-    columns on the tensor-core tiles, 256 on the CUDA cores)."""
-    limit = 128 if sixteen_bit and spec.head_dim % 8 == 0 and spec.v_head_dim % 8 == 0 and spec.head_dim <= 128 else 256
+    columns on the tensor-core tiles that serve 16-bit prompt portions, 256 on the CUDA-core kernels that serve fp32
+    and single tokens)."""
+    limit = 128 if tensor_tiles and spec.head_dim % 8 == 0 and spec.v_head_dim % 8 == 0 and spec.head_dim <= 128 else 256
     best = 1
     for c in range(1, spec.kv_heads + 1):
         if spec.kv_heads % c == 0 and c * spec.v_head_dim <= limit:
@@ -354,7 +355,7 @@ def conv_window_attention(li: int, spec: ConvWindowAttentionSpec, w: dict[str, t
                            b.seq_start, b.seq_ctx, b.seq_slot, activation=False)
     ones = w["ones"] if L.qk_unit_rms else None
     head_norm_rope_prepare(qkv, pool, b.kv_rows, None, ones, ones, H, G, D, Dv, 0, eps)
-    per_call = wide_value_heads(L, qkv.dtype != torch.float32) if L.head_mix else 0
+    per_call = wide_value_heads(L, qkv.dtype != torch.float32 and b.num_portions > 0) if L.head_mix else 0
     calls = G // per_call if L.head_mix else 1
     width = per_call * Dv if L.head_mix else Dv
     att = torch.empty((b.tokens, calls * H * width), dtype=qkv.dtype, device=qkv.device)
