@@ -11,9 +11,9 @@
 //
 // Four neighbouring lanes share one value column of one head and hold a quarter of its D memory entries each in
 // registers, so the two contractions over D of a token (S^T k, S^T q) are sums inside a thread plus two shuffles.  A
-// CTA = (64 value columns, head, sequence) stages 16 tokens at a time: the token's gates, unit norms and scalars are
-// evaluated in fp32 by the warps in parallel and left in shared memory with the chunk's v columns, then the 16
-// updates run back to back.  A sequence without cached tokens starts from zero and never
+// CTA = (64 value columns, head, sequence) stages 16 tokens at a time in one of two buffers: the token's gates, unit
+// norms and scalars are evaluated in fp32 by the warps in parallel and left in shared memory with the round's v
+// columns; the next round's rows are fetched into registers before the current round's 16 updates run back to back.  A sequence without cached tokens starts from zero and never
 // reads its slot; every sequence writes its slot at the end of the step.
 //
 //   head_norm_gate   out[t, h, :] = unit_rms(y[t, h, :]) * w * (silu(gate[t, h, :]) or 1): the per-head output norm
@@ -57,17 +57,24 @@ __global__ void __launch_bounds__(kScanThreads) gated_linear_scan_kernel(GlaArgs
   pdl_prologue();
   constexpr int R4 = DP / 16;                       // float4 groups of memory rows per thread
   constexpr int COLS = kScanThreads / kParts;
-  __shared__ __align__(16) float qs[kTok * DP];
-  __shared__ __align__(16) float ks[kTok * DP];     // mode 1: unit keys; mode 0: forget gates
-  __shared__ float vs[kTok * COLS];
-  __shared__ float sc[kTok * 2];                    // mode 1: (g, beta) per token
+  constexpr int TOK = DP > 128 ? 8 : kTok;          // tokens per round
+  constexpr int NW = kScanThreads / 32;
+  constexpr int TPW = TOK / NW;                     // tokens a warp prepares per round
+  constexpr int NI = (DP + 31) / 32;
+  constexpr int NV = TOK * COLS / kScanThreads;     // v entries a thread fetches per round
+  // two rounds of staged tokens: the next round's rows are fetched into registers before the current round's updates
+  // run, and prepared (gates, unit norms) into the other buffer after them, so their latency hides behind the updates
+  __shared__ __align__(16) float qs[2][TOK * DP];
+  __shared__ __align__(16) float ks[2][TOK * DP];   // mode 1: unit keys; mode 0: forget gates
+  __shared__ float vs[2][TOK * COLS];
+  __shared__ float sc[2][TOK * 2];                  // mode 1: (g, beta) per token
   const int D = a.D, V = a.V, H = a.H;
   const int h = blockIdx.y, s = blockIdx.z;
   const int qh = h / (H / a.QH);
   const int part = threadIdx.x & (kParts - 1), lcol = threadIdx.x / kParts;
   const int col = blockIdx.x * COLS + lcol;
   const bool live = col < V;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int start = a.seq_start[s], len = a.seq_start[s + 1] - start, ctx = a.seq_ctx[s];
   const int64_t slot = a.seq_slot[s];
   float* sp = a.state + ((slot * H + h) * (int64_t)D) * V;
@@ -86,60 +93,89 @@ __global__ void __launch_bounds__(kScanThreads) gated_linear_scan_kernel(GlaArgs
   const T* vp = (const T*)a.v;
   float neg_a = 0.f, dtb = 0.f;
   if (MODE == 1) { neg_a = -expf(to_f32(((const T*)a.c1)[h])); dtb = to_f32(((const T*)a.c0)[h]); }
-  for (int t0 = 0; t0 < len; t0 += kTok) {
-    const int nt = min(kTok, len - t0);
-    __syncthreads();                                 // the previous round's readers are done
-    for (int t = warp; t < nt; t += nw) {
+  float lo[NI];                                      // mode 0: this lane's lower bounds
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    const int d = lane + 32 * i;
+    lo[i] = (MODE == 0 && d < D) ? to_f32(((const T*)a.c0)[h * D + d]) : 0.f;
+  }
+  float rq[TPW][NI], rk[TPW][NI], rs0[TPW], rs1[TPW], rv[NV];
+
+  auto fetch = [&](int t0) {                         // raw rows of round t0 -> registers (loads stay in flight)
+    const int nt = min(TOK, len - t0);
+#pragma unroll
+    for (int j = 0; j < TPW; ++j) {
+      const int t = warp + NW * j;
       const int64_t row = start + t0 + t;
+      const int hq = MODE == 1 ? qh : h;
+#pragma unroll
+      for (int i = 0; i < NI; ++i) {
+        const int d = lane + 32 * i;
+        const bool in = t < nt && d < D;
+        rq[j][i] = in ? to_f32(qp[row * a.q_stride + hq * D + d]) : 0.f;
+        rk[j][i] = in ? to_f32(kp[row * a.k_stride + hq * D + d]) : 0.f;
+      }
+      rs0[j] = rs1[j] = 0.f;
+      if (MODE == 1 && t < nt && lane == 0) {
+        rs0[j] = to_f32(((const T*)a.p0)[row * a.p0_stride + h]);
+        rs1[j] = to_f32(((const T*)a.p1)[row * a.p1_stride + h]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = threadIdx.x + kScanThreads * j;
+      const int t = i / COLS, c = blockIdx.x * COLS + (i - t * COLS);
+      rv[j] = (t < nt && c < V) ? to_f32(vp[(int64_t)(start + t0 + t) * a.v_stride + h * V + c]) : 0.f;
+    }
+  };
+  auto stage = [&](int buf) {                        // registers -> gates / unit vectors in shared memory
+#pragma unroll
+    for (int j = 0; j < TPW; ++j) {
+      const int t = warp + NW * j;
       if (MODE == 1) {
-        float qv[(DP + 31) / 32], kv[(DP + 31) / 32], sq = 0.f, sk = 0.f;
+        float sq = 0.f, sk = 0.f;
 #pragma unroll
-        for (int i = 0; i < (DP + 31) / 32; ++i) {
-          const int d = lane + 32 * i;
-          qv[i] = d < D ? to_f32(qp[row * a.q_stride + qh * D + d]) : 0.f;
-          kv[i] = d < D ? to_f32(kp[row * a.k_stride + qh * D + d]) : 0.f;
-          sq = fmaf(qv[i], qv[i], sq);
-          sk = fmaf(kv[i], kv[i], sk);
-        }
-        const float rq = a.q_scale / sqrtf(warp_reduce_sum(sq) + a.unit_eps);
-        const float rk = 1.0f / sqrtf(warp_reduce_sum(sk) + a.unit_eps);
+        for (int i = 0; i < NI; ++i) { sq = fmaf(rq[j][i], rq[j][i], sq); sk = fmaf(rk[j][i], rk[j][i], sk); }
+        const float nq = a.q_scale / sqrtf(warp_reduce_sum(sq) + a.unit_eps);
+        const float nk = 1.0f / sqrtf(warp_reduce_sum(sk) + a.unit_eps);
 #pragma unroll
-        for (int i = 0; i < (DP + 31) / 32; ++i) {
+        for (int i = 0; i < NI; ++i) {
           const int d = lane + 32 * i;
-          if (d < DP) { qs[t * DP + d] = qv[i] * rq; ks[t * DP + d] = kv[i] * rk; }
+          if (d < DP) { qs[buf][t * DP + d] = rq[j][i] * nq; ks[buf][t * DP + d] = rk[j][i] * nk; }
         }
         if (lane == 0) {
-          const float dt = gla_softplus(to_f32(((const T*)a.p1)[row * a.p1_stride + h]) + dtb);
-          sc[2 * t] = expf(neg_a * dt);
-          sc[2 * t + 1] = gla_sigmoid(to_f32(((const T*)a.p0)[row * a.p0_stride + h]));
+          sc[buf][2 * t] = expf(neg_a * gla_softplus(rs1[j] + dtb));
+          sc[buf][2 * t + 1] = gla_sigmoid(rs0[j]);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < (DP + 31) / 32; ++i) {
+        for (int i = 0; i < NI; ++i) {
           const int d = lane + 32 * i;
-          float qv = 0.f, f = 1.f;                   // rows beyond D: nothing written, nothing read
-          if (d < D) {
-            qv = gla_silu(to_f32(qp[row * a.q_stride + h * D + d]));
-            const float lo = to_f32(((const T*)a.c0)[h * D + d]);
-            f = lo + (1.0f - lo) * gla_sigmoid(to_f32(kp[row * a.k_stride + h * D + d]));
-          }
-          if (d < DP) { qs[t * DP + d] = qv; ks[t * DP + d] = f; }
+          // rows beyond D: nothing written (f = 1 keeps the zero), nothing read (q = 0)
+          const float f = d < D ? lo[i] + (1.0f - lo[i]) * gla_sigmoid(rk[j][i]) : 1.f;
+          if (d < DP) { qs[buf][t * DP + d] = d < D ? gla_silu(rq[j][i]) : 0.f; ks[buf][t * DP + d] = f; }
         }
       }
     }
-    for (int i = threadIdx.x; i < nt * COLS; i += kScanThreads) {
-      const int t = i / COLS, c = blockIdx.x * COLS + (i - t * COLS);
-      vs[i] = c < V ? to_f32(vp[(int64_t)(start + t0 + t) * a.v_stride + h * V + c]) : 0.f;
-    }
-    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < NV; ++j) vs[buf][threadIdx.x + kScanThreads * j] = rv[j];
+  };
+
+  if (len > 0) { fetch(0); stage(0); }
+  __syncthreads();
+  int buf = 0;
+  for (int t0 = 0; t0 < len; t0 += TOK, buf ^= 1) {
+    const int nt = min(TOK, len - t0);
+    const bool more = t0 + TOK < len;
+    if (more) fetch(t0 + TOK);
 #pragma unroll 2
     for (int t = 0; t < nt; ++t) {
-      const float4* q4 = reinterpret_cast<const float4*>(qs + t * DP) + part;
-      const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP) + part;
-      const float x = vs[t * COLS + lcol];
+      const float4* q4 = reinterpret_cast<const float4*>(qs[buf] + t * DP) + part;
+      const float4* k4 = reinterpret_cast<const float4*>(ks[buf] + t * DP) + part;
+      const float x = vs[buf][t * COLS + lcol];
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
       if (MODE == 1) {
-        const float g = sc[2 * t], beta = sc[2 * t + 1];
+        const float g = sc[buf][2 * t], beta = sc[buf][2 * t + 1];
         float4 kk[R4];
         float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
@@ -175,6 +211,8 @@ __global__ void __launch_bounds__(kScanThreads) gated_linear_scan_kernel(GlaArgs
       o += __shfl_xor_sync(0xffffffffu, o, 2);
       if (live && part == 0) a.y[(int64_t)(start + t0 + t) * H * V + h * V + col] = o;
     }
+    if (more) stage(buf ^ 1);
+    __syncthreads();
   }
   if (live) {
 #pragma unroll
