@@ -968,19 +968,17 @@ def gofezen_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) 
         lambda: K.head_mix(wide, talk, H, G, per_call, D), nbytes=T * H * D * (G + 1) * es)
     keys = min(ctx + 1, win)
     splits, per = split_plan(keys)
-    # a step of single tokens runs on the CUDA-core kernel, which takes 256 value columns per call
+    # a step of single tokens runs on the CUDA-core kernel, which takes blocks of up to 256 value columns
     d_per_call = max(c for c in range(1, G + 1) if G % c == 0 and (c * D <= 256 or c == 1))
     d_calls, d_width = G // d_per_call, d_per_call * D
 
     def mixed_decode():
-        for cidx in range(d_calls):
-            K.sink_attention(wide[:batch, cidx * H * d_width:(cidx + 1) * H * d_width], proj, pool, tab, d_start, d_ctx, p_slot,
-                             None, batch, 1, None, H, G, D, d_width, scale, 0.0, num_splits=splits, split_keys=per, window=win,
-                             v_col0=G * D + cidx * d_width, v_head_stride=0)
+        K.sink_attention(wide[:batch], proj, pool, tab, d_start, d_ctx, p_slot, None, batch, 1, None, H, G, D, d_width, scale,
+                         0.0, num_splits=splits, split_keys=per, window=win, v_col0=G * D, v_head_stride=0, v_blocks=d_calls)
 
     lkeys = min(ctx + 1, ctx % chunk + 1)
     lsplits, lper = split_plan(min(ctx + 1, chunk))
-    add("window attention over wide values (decode, %d of %d keys seen, %d calls)" % (keys, ctx + 1, d_calls),
+    add("window attention over wide values (decode, %d of %d keys seen, %d value blocks in one call)" % (keys, ctx + 1, d_calls),
         "block-masked attention (decode, %d keys seen)" % lkeys, mixed_decode, nbytes=batch * keys * kvw * es,
         like_fn=lambda: K.sink_attention(out, proj, pool, tab, d_start, d_ctx, p_slot, None, batch, 1, None, H, G, D, D, scale,
                                          30.0, num_splits=lsplits, split_keys=lper, block=chunk),

@@ -377,14 +377,16 @@ int b2l_attn_prepare(void* qkv, int64_t qkv_row_stride, void* kv_pool, int64_t k
  * (from the first one it sees) are cut into num_splits ranges of split_keys and merged (workspace:
  * b2l_sink_attention_workspace_bytes).  window > 0: token p sees keys p - window + 1 .. p only; block > 0 (window <= 0):
  * token p sees keys floor(p / block) * block .. p only.  v_col0 < 0: a pool
- * row is [keys | values]; v_col0 >= 0: the values start at that column (0: they are the keys' leading columns). */
+ * row is [keys | values]; v_col0 >= 0: the values start at that column (0: they are the keys' leading columns).
+ * v_blocks > 1 (num_splits > 0 only): v_blocks neighbouring blocks of v_head_dim value columns in one call, each as
+ * `heads` more results (out [v_blocks][heads][v_head_dim] per token; workspace for heads * v_blocks heads). */
 int64_t b2l_sink_attention_workspace_bytes(int64_t num_seqs, int heads, int v_head_dim, int num_splits);
 int b2l_sink_attention(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride, const void* kv_pool,
                        int64_t kv_row_stride, const void* table_i32, int64_t table_row_stride, const void* seq_start,
                        const void* seq_ctx, const void* seq_slot, const void* seq_list, int64_t num_seqs,
                        int max_q_len, const void* sink, int heads, int kv_heads, int head_dim, int v_head_dim,
                        float scale, float softcap, int window, int block, int v_col0, int v_head_stride,
-                       int num_splits, int split_keys, void* workspace, int64_t workspace_bytes, int dtype,
+                       int v_blocks, int num_splits, int split_keys, void* workspace, int64_t workspace_bytes, int dtype,
                        void* stream);
 
 /* Parallel-block layer-list models with a depth-weighted residual stack (csrc/parallel_stream.cu).

@@ -43,6 +43,8 @@ struct AttnArgs {
   int v_hstride;               // columns between the values of neighbouring kv heads (Dv; 0: every kv head reads the
                                // same Dv value columns, e.g. ALL value heads side by side as one wide head)
   int block;                   // > 0 (and no window): block-diagonal mask, see first_visible
+  int v_blocks;                // split mode: one launch covers v_blocks blocks of Dv value columns (block c starts c * Dv
+                               // columns after v_col0), each as H more heads: results [v_blocks][H][Dv] per token
   int head_rows;               // tensor-core kernel, one new token per sequence: the tile's rows are the query HEADS of
                                // one kv head (not tokens), blockIdx.x is a key range, results go to `part`
   float scale, softcap;
@@ -483,8 +485,10 @@ __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
   const int start = a.seq_start[s], ctx = a.seq_ctx[s];
   const int64_t slot = a.seq_slot[s];
   const int hchunks = (per + kSplitRows - 1) / kSplitRows;
-  const int g = blockIdx.y / hchunks, h_first = g * per + (blockIdx.y % hchunks) * kSplitRows;
+  const int vb = blockIdx.y / (a.G * hchunks), by = blockIdx.y - vb * (a.G * hchunks);
+  const int g = by / hchunks, h_first = g * per + (by % hchunks) * kSplitRows;
   const int h_count = min(kSplitRows, g * per + per - h_first);
+  const int v_col = a.v_col0 + vb * Dv + g * a.v_hstride;                    // first value column of this CTA
   const int win_lo = max(0, first_visible(a, ctx));                          // the new token's first visible key
   const int key_lo = win_lo + blockIdx.x * a.chunk, key_hi = min(key_lo + a.chunk, ctx + 1);
   const T* q = (const T*)a.q;
@@ -505,7 +509,7 @@ __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
   const int* trow = a.table + slot * a.table_stride;
   const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
   const bool vec_ok = (D % VEC == 0) && (Dv % VEC == 0) && (a.kv_stride % VEC == 0) && (a.v_col0 % VEC == 0) &&
-                      (((uintptr_t)a.kv % 16) == 0);
+                      (a.v_hstride % VEC == 0) && (((uintptr_t)a.kv % 16) == 0);
   for (int k0 = key_lo + warp * 32; k0 < key_hi; k0 += 128) {
     const int nk = min(32, key_hi - k0);
     __syncwarp();
@@ -531,7 +535,7 @@ __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
         }
       };
       stage_rows(ks, Dp, g * D, D / VEC);
-      stage_rows(vs, Dvp, a.v_col0 + g * a.v_hstride, Dv / VEC);
+      stage_rows(vs, Dvp, v_col, Dv / VEC);
     } else {
       for (int i = lane; i < nk * D; i += 32) {
         const int j = i / D, d = i - j * D;
@@ -539,7 +543,7 @@ __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
       }
       for (int i = lane; i < nk * Dv; i += 32) {
         const int j = i / Dv, d = i - j * Dv;
-        vs[j * Dvp + d] = kv[(int64_t)trow[k0 + j] * a.kv_stride + a.v_col0 + g * a.v_hstride + d];
+        vs[j * Dvp + d] = kv[(int64_t)trow[k0 + j] * a.kv_stride + v_col + d];
       }
     }
     __syncwarp();
@@ -620,7 +624,7 @@ __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
       sc4[w] = mw == -INFINITY ? 0.f : expf(mw - mf);
       den += mrg[(w * kSplitRows + r) * (2 + Dv) + 1] * sc4[w];
     }
-    float* dst = a.part + (((int64_t)z * a.H + h_first + r) * a.nsplit + blockIdx.x) * (Dv + 2);
+    float* dst = a.part + ((((int64_t)z * a.v_blocks + vb) * a.H + h_first + r) * a.nsplit + blockIdx.x) * (Dv + 2);
     if (lane == 0) { dst[0] = mf; dst[1] = den; }
     for (int d = lane; d < Dv; d += 32) {
       float v = 0.f;
@@ -643,7 +647,7 @@ int launch_attention_split(const AttnArgs& a, int64_t num_seqs, cudaStream_t st)
   const int dvj = (a.Dv + 31) / 32;
   B2L_REQUIRE(dvj <= 8, "sink_attention: value head size %d > 256", a.Dv);
   const int per = a.H / a.G, hchunks = (per + kSplitRows - 1) / kSplitRows;
-  const dim3 grid((unsigned)a.nsplit, (unsigned)(a.G * hchunks), (unsigned)num_seqs);
+  const dim3 grid((unsigned)a.nsplit, (unsigned)(a.G * hchunks * a.v_blocks), (unsigned)num_seqs);
 #define B2L_SPLIT(J)                                                                                     \
   do {                                                                                                   \
     static int cache[64] = {0};                                                                          \
@@ -668,7 +672,7 @@ __global__ void __launch_bounds__(64) sink_attention_merge_kernel(T* __restrict_
                                                                   const T* __restrict__ sink,
                                                                   const int* __restrict__ seq_start,
                                                                   const int* __restrict__ seq_list, int H, int Dv,
-                                                                  int nsplit) {
+                                                                  int nsplit, int sink_heads) {
   pdl_prologue();
   __shared__ float wsm[kMergeCached];
   __shared__ float red[2];
@@ -681,7 +685,7 @@ __global__ void __launch_bounds__(64) sink_attention_merge_kernel(T* __restrict_
   if (lane == 0) red[warp] = mf;
   __syncthreads();
   mf = fmaxf(red[0], red[1]);
-  if (sink) mf = fmaxf(mf, to_f32(sink[h]));
+  if (sink) mf = fmaxf(mf, to_f32(sink[h % sink_heads]));
   __syncthreads();
   float den = 0.f;
   for (int i = tid; i < nsplit; i += 64) {
@@ -693,7 +697,7 @@ __global__ void __launch_bounds__(64) sink_attention_merge_kernel(T* __restrict_
   if (lane == 0) red[warp] = den;
   __syncthreads();
   den = red[0] + red[1];
-  if (sink) den += expf(to_f32(sink[h]) - mf);
+  if (sink) den += expf(to_f32(sink[h % sink_heads]) - mf);
   T* o = out + (int64_t)seq_start[s] * out_stride + h * Dv;
   for (int d = tid; d < Dv; d += 64) {
     float v = 0.f;
@@ -911,13 +915,16 @@ extern "C" int64_t b2l_sink_attention_workspace_bytes(int64_t num_seqs, int head
  * and `split_keys` keys go to each of the num_splits ranges, counted from the token's first visible key
  * (num_splits * split_keys >= the most keys any listed token sees: context + 1, or the window if that is smaller).
  * window <= 0: no sliding window; block > 0 (window <= 0): block-diagonal mask; v_col0 < 0: the values follow the keys in a pool row (column kv_heads * head_dim);
- * v_head_stride < 0: kv head g's values start g * v_head_dim columns after v_col0 (0: all kv heads read the same columns). */
+ * v_head_stride < 0: kv head g's values start g * v_head_dim columns after v_col0 (0: all kv heads read the same columns).
+ * v_blocks > 1 (split mode): block c of v_head_dim value columns starts c * v_head_dim columns further and is one more
+ * set of `heads` results, out [v_blocks][heads][v_head_dim] per token, in the same two launches (workspace for
+ * heads * v_blocks heads). */
 extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride,
                                   const void* kv_pool, int64_t kv_row_stride, const void* table_i32,
                                   int64_t table_row_stride, const void* seq_start, const void* seq_ctx,
                                   const void* seq_slot, const void* seq_list, int64_t num_seqs, int max_q_len,
                                   const void* sink, int heads, int kv_heads, int head_dim, int v_head_dim, float scale,
-                                  float softcap, int window, int block, int v_col0, int v_head_stride,
+                                  float softcap, int window, int block, int v_col0, int v_head_stride, int v_blocks,
                                   int num_splits, int split_keys, void* workspace, int64_t workspace_bytes, int dtype, void* stream) {
   B2L_REQUIRE(out && q && kv_pool && table_i32 && seq_start && seq_ctx && seq_slot, "sink_attention: null pointer");
   B2L_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "sink_attention: %d heads must be a multiple of num_kv_heads %d",
@@ -941,17 +948,19 @@ extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void*
   a.v_col0 = v_col0 >= 0 ? v_col0 : kv_heads * head_dim;
   a.v_hstride = v_head_stride >= 0 ? v_head_stride : v_head_dim;
   a.head_rows = 0;
+  a.v_blocks = v_blocks > 1 ? v_blocks : 1;
+  B2L_REQUIRE(a.v_blocks == 1 || num_splits > 0, "sink_attention: value blocks are for steps of single tokens");
   const int hchunks = (per + a.PH - 1) / a.PH;
   if (num_splits > 0) {
     B2L_REQUIRE(split_keys > 0, "sink_attention: split_keys must be positive");
-    const int64_t need = b2l_sink_attention_workspace_bytes(num_seqs, heads, v_head_dim, num_splits);
+    const int64_t need = b2l_sink_attention_workspace_bytes(num_seqs, heads * a.v_blocks, v_head_dim, num_splits);
     B2L_REQUIRE(workspace && workspace_bytes >= need, "sink_attention: workspace too small (%lld < %lld)",
                 (long long)workspace_bytes, (long long)need);
     int rc = B2L_OK;
     // many query heads per kv head (latent caches: ALL heads share one row): the heads become the rows of a tensor-core
     // tile, so a cached row is read once and scored against every head by mma instead of 4 heads at a time on the
     // CUDA cores; same partials, same merge
-    if (per > kSplitRows && mma_path_ok(a, dtype)) {
+    if (per > kSplitRows && a.v_blocks == 1 && mma_path_ok(a, dtype)) {
       a.head_rows = 1;
       rc = dtype == B2L_F16 ? dispatch_attention_mma<__half>(a, 1, num_seqs, st)
                             : dispatch_attention_mma<__nv_bfloat16>(a, 1, num_seqs, st);
@@ -960,9 +969,9 @@ extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void*
     }
     if (rc != B2L_OK) return rc;
     B2L_DISPATCH_FLOAT(dtype, "sink_attention", {
-      b2l_launch(sink_attention_merge_kernel<T>, dim3((unsigned)heads, (unsigned)num_seqs), dim3(64), (size_t)0, st,
-                 (T*)out, out_row_stride, (const float*)workspace, (const T*)sink, (const int*)seq_start,
-                 (const int*)seq_list, heads, v_head_dim, num_splits);
+      b2l_launch(sink_attention_merge_kernel<T>, dim3((unsigned)(heads * a.v_blocks), (unsigned)num_seqs), dim3(64),
+                 (size_t)0, st, (T*)out, out_row_stride, (const float*)workspace, (const T*)sink,
+                 (const int*)seq_start, (const int*)seq_list, heads * a.v_blocks, v_head_dim, num_splits, heads);
     });
     B2L_LAUNCH_CHECK();
     return B2L_OK;

@@ -9,11 +9,14 @@
 //                          S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 //                          (the read-out sees the current token's write)
 //
-// Four neighbouring lanes share one value column of one head and hold a quarter of its D memory entries each in
-// registers, so the two contractions over D of a token (S^T k, S^T q) are sums inside a thread plus two shuffles.  A
-// CTA = (64 value columns, head, sequence) stages 16 tokens at a time in one of two buffers: the token's gates, unit
-// norms and scalars are evaluated in fp32 by the warps in parallel and left in shared memory with the round's v
-// columns; the next round's rows are fetched into registers before the current round's 16 updates run back to back.  A sequence without cached tokens starts from zero and never
+// 4 to 16 neighbouring lanes share one value column of one head and hold at most 16 of its D memory entries each in
+// registers, so a contraction over D (S^T k, S^T q) is a sum inside a thread plus a few shuffles, and a thread needs
+// about 64 registers: 32 warps are resident on an SM and hide the token-to-token dependency.  The delta rule's two
+// contractions both read the memory before the token's write (S'^T q = g S^T q + u (k . q)), so they run side by side.
+// A CTA = (256 / lanes value columns, head, sequence) stages 16 tokens at a time in one of two buffers: the token's
+// gates, unit norms and scalars are evaluated in fp32 by the warps in parallel and left in shared memory with the
+// round's v columns; the next round's rows are fetched into registers before the current round's 16 updates run back
+// to back.  A sequence without cached tokens starts from zero and never
 // reads its slot; every sequence writes its slot at the end of the step.
 //
 //   head_norm_gate   out[t, h, :] = unit_rms(y[t, h, :]) * w * (silu(gate[t, h, :]) or 1): the per-head output norm
@@ -49,56 +52,56 @@ struct GlaArgs {
   float q_scale, unit_eps;
 };
 
-constexpr int kParts = 4;                 // threads that share one value column (neighbouring lanes), each with DP / 4 rows
 constexpr int kScanThreads = 256;
+// lanes that share one value column (neighbouring lanes): each holds at most 16 memory rows, so a thread stays near 64
+// registers and four CTAs (32 warps) are resident on an SM to hide the token-to-token dependency
+constexpr int scan_parts(int dp) { return dp <= 64 ? 4 : dp / 16; }
 
-template <typename T, int DP, int MODE>
-__global__ void __launch_bounds__(kScanThreads) gated_linear_scan_kernel(GlaArgs a) {
+template <typename T, int DP, int MODE, int C>
+__global__ void __launch_bounds__(kScanThreads, 2) gated_linear_scan_kernel(GlaArgs a) {
   pdl_prologue();
-  constexpr int R4 = DP / 16;                       // float4 groups of memory rows per thread
-  constexpr int COLS = kScanThreads / kParts;
+  constexpr int PARTS = scan_parts(DP);
+  constexpr int R4 = DP / (4 * PARTS);              // float4 groups of memory rows per thread
+  // C value columns per thread: a staged k / q entry read from shared memory feeds C memories
+  constexpr int COLS = kScanThreads / PARTS * C;
   constexpr int TOK = DP > 128 ? 8 : kTok;          // tokens per round
   constexpr int NW = kScanThreads / 32;
   constexpr int TPW = TOK / NW;                     // tokens a warp prepares per round
   constexpr int NI = (DP + 31) / 32;
-  constexpr int NV = TOK * COLS / kScanThreads;     // v entries a thread fetches per round
+  constexpr int NA = C == 1 ? 4 : 2;                // partial sums of a contraction inside a thread (chains of D / (PARTS NA) products)
+  constexpr int NV = (TOK * COLS + kScanThreads - 1) / kScanThreads;   // v entries a thread fetches per round
   // two rounds of staged tokens: the next round's rows are fetched into registers before the current round's updates
   // run, and prepared (gates, unit norms) into the other buffer after them, so their latency hides behind the updates
   __shared__ __align__(16) float qs[2][TOK * DP];
   __shared__ __align__(16) float ks[2][TOK * DP];   // mode 1: unit keys; mode 0: forget gates
   __shared__ float vs[2][TOK * COLS];
-  __shared__ float sc[2][TOK * 2];                  // mode 1: (g, beta) per token
+  __shared__ float sc[2][TOK * 4];                  // mode 1: (g, beta, k . q) per token
   const int D = a.D, V = a.V, H = a.H;
   const int h = blockIdx.y, s = blockIdx.z;
   const int qh = h / (H / a.QH);
-  const int part = threadIdx.x & (kParts - 1), lcol = threadIdx.x / kParts;
-  const int col = blockIdx.x * COLS + lcol;
-  const bool live = col < V;
+  const int part = threadIdx.x & (PARTS - 1), lcol = threadIdx.x / PARTS * C;
+  const int col = blockIdx.x * COLS + lcol;          // the thread's first column
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int start = a.seq_start[s], len = a.seq_start[s + 1] - start, ctx = a.seq_ctx[s];
   const int64_t slot = a.seq_slot[s];
   float* sp = a.state + ((slot * H + h) * (int64_t)D) * V;
-  // thread (col, part) holds rows d = 16 i + 4 part + e (i < R4, e < 4): the four parts of a column read four
-  // neighbouring float4 of a staged vector, so a warp's reads fall in different banks
-  float S[R4 * 4];
+  // thread (col, part) holds rows d = 4 PARTS i + 4 part + e (i < R4, e < 4): the parts of a column read neighbouring
+  // float4 of a staged vector, so a warp's reads fall in different banks
+  float S[C][R4 * 4];
 #pragma unroll
-  for (int i = 0; i < R4; ++i)
+  for (int c = 0; c < C; ++c)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int d = 16 * i + 4 * part + e;
-      S[4 * i + e] = (ctx > 0 && live && d < D) ? sp[(int64_t)d * V + col] : 0.f;
-    }
+    for (int i = 0; i < R4; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int d = 4 * PARTS * i + 4 * part + e;
+        S[c][4 * i + e] = (ctx > 0 && col + c < V && d < D) ? sp[(int64_t)d * V + col + c] : 0.f;
+      }
   const T* qp = (const T*)a.q;
   const T* kp = (const T*)a.k;
   const T* vp = (const T*)a.v;
   float neg_a = 0.f, dtb = 0.f;
   if (MODE == 1) { neg_a = -expf(to_f32(((const T*)a.c1)[h])); dtb = to_f32(((const T*)a.c0)[h]); }
-  float lo[NI];                                      // mode 0: this lane's lower bounds
-#pragma unroll
-  for (int i = 0; i < NI; ++i) {
-    const int d = lane + 32 * i;
-    lo[i] = (MODE == 0 && d < D) ? to_f32(((const T*)a.c0)[h * D + d]) : 0.f;
-  }
   float rq[TPW][NI], rk[TPW][NI], rs0[TPW], rs1[TPW], rv[NV];
 
   auto fetch = [&](int t0) {                         // raw rows of round t0 -> registers (loads stay in flight)
@@ -133,32 +136,45 @@ __global__ void __launch_bounds__(kScanThreads) gated_linear_scan_kernel(GlaArgs
     for (int j = 0; j < TPW; ++j) {
       const int t = warp + NW * j;
       if (MODE == 1) {
-        float sq = 0.f, sk = 0.f;
+        float sq = 0.f, sk = 0.f, qk = 0.f;
 #pragma unroll
-        for (int i = 0; i < NI; ++i) { sq = fmaf(rq[j][i], rq[j][i], sq); sk = fmaf(rk[j][i], rk[j][i], sk); }
+        for (int i = 0; i < NI; ++i) {
+          sq = fmaf(rq[j][i], rq[j][i], sq); sk = fmaf(rk[j][i], rk[j][i], sk); qk = fmaf(rq[j][i], rk[j][i], qk);
+        }
         const float nq = a.q_scale / sqrtf(warp_reduce_sum(sq) + a.unit_eps);
         const float nk = 1.0f / sqrtf(warp_reduce_sum(sk) + a.unit_eps);
+        qk = warp_reduce_sum(qk) * nq * nk;
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
           const int d = lane + 32 * i;
           if (d < DP) { qs[buf][t * DP + d] = rq[j][i] * nq; ks[buf][t * DP + d] = rk[j][i] * nk; }
         }
         if (lane == 0) {
-          sc[buf][2 * t] = expf(neg_a * gla_softplus(rs1[j] + dtb));
-          sc[buf][2 * t + 1] = gla_sigmoid(rs0[j]);
+          sc[buf][4 * t] = expf(neg_a * gla_softplus(rs1[j] + dtb));
+          sc[buf][4 * t + 1] = gla_sigmoid(rs0[j]);
+          sc[buf][4 * t + 2] = qk;
         }
       } else {
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
           const int d = lane + 32 * i;
           // rows beyond D: nothing written (f = 1 keeps the zero), nothing read (q = 0)
-          const float f = d < D ? lo[i] + (1.0f - lo[i]) * gla_sigmoid(rk[j][i]) : 1.f;
+          const float lo = d < D ? to_f32(((const T*)a.c0)[h * D + d]) : 0.f;
+          const float f = d < D ? lo + (1.0f - lo) * gla_sigmoid(rk[j][i]) : 1.f;
           if (d < DP) { qs[buf][t * DP + d] = d < D ? gla_silu(rq[j][i]) : 0.f; ks[buf][t * DP + d] = f; }
         }
       }
     }
 #pragma unroll
-    for (int j = 0; j < NV; ++j) vs[buf][threadIdx.x + kScanThreads * j] = rv[j];
+    for (int j = 0; j < NV; ++j) {
+      const int i = threadIdx.x + kScanThreads * j;
+      if (i < TOK * COLS) vs[buf][i] = rv[j];
+    }
+  };
+  auto column_sum = [&](float x) {                   // over the lanes of one column
+#pragma unroll
+    for (int m = 1; m < PARTS; m <<= 1) x += __shfl_xor_sync(0xffffffffu, x, m);
+    return x;
   };
 
   if (len > 0) { fetch(0); stage(0); }
@@ -172,57 +188,82 @@ __global__ void __launch_bounds__(kScanThreads) gated_linear_scan_kernel(GlaArgs
     for (int t = 0; t < nt; ++t) {
       const float4* q4 = reinterpret_cast<const float4*>(qs[buf] + t * DP) + part;
       const float4* k4 = reinterpret_cast<const float4*>(ks[buf] + t * DP) + part;
-      const float x = vs[buf][t * COLS + lcol];
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      float x[C], o[C];
+#pragma unroll
+      for (int c = 0; c < C; ++c) x[c] = vs[buf][t * COLS + lcol + c];
       if (MODE == 1) {
-        const float g = sc[buf][2 * t], beta = sc[buf][2 * t + 1];
+        // both contractions read the memory BEFORE the token's write, so they run side by side:
+        //   S' = g S + k u^T,  u = beta (v - g S^T k);   S'^T q = g S^T q + u (k . q)
+        const float g = sc[buf][4 * t], beta = sc[buf][4 * t + 1], kq = sc[buf][4 * t + 2];
         float4 kk[R4];
-        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+        float dk[C][NA], dq[C][NA];
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+#pragma unroll
+          for (int e = 0; e < NA; ++e) dk[c][e] = dq[c][e] = 0.f;
 #pragma unroll
         for (int i = 0; i < R4; ++i) {
-          kk[i] = k4[4 * i];
-          d0 = fmaf(S[4 * i], kk[i].x, d0); d1 = fmaf(S[4 * i + 1], kk[i].y, d1);
-          d2 = fmaf(S[4 * i + 2], kk[i].z, d2); d3 = fmaf(S[4 * i + 3], kk[i].w, d3);
+          kk[i] = k4[PARTS * i];
+          const float4 qq = q4[PARTS * i];
+#pragma unroll
+          for (int c = 0; c < C; ++c) {
+            dk[c][0] = fmaf(S[c][4 * i], kk[i].x, dk[c][0]); dk[c][1] = fmaf(S[c][4 * i + 1], kk[i].y, dk[c][1]);
+            dk[c][2 % NA] = fmaf(S[c][4 * i + 2], kk[i].z, dk[c][2 % NA]); dk[c][3 % NA] = fmaf(S[c][4 * i + 3], kk[i].w, dk[c][3 % NA]);
+            dq[c][0] = fmaf(S[c][4 * i], qq.x, dq[c][0]); dq[c][1] = fmaf(S[c][4 * i + 1], qq.y, dq[c][1]);
+            dq[c][2 % NA] = fmaf(S[c][4 * i + 2], qq.z, dq[c][2 % NA]); dq[c][3 % NA] = fmaf(S[c][4 * i + 3], qq.w, dq[c][3 % NA]);
+          }
         }
-        float dot = (d0 + d1) + (d2 + d3);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-        const float u = beta * (x - g * dot);
 #pragma unroll
-        for (int i = 0; i < R4; ++i) {
-          const float4 qq = q4[4 * i];
-          S[4 * i] = fmaf(g, S[4 * i], kk[i].x * u); S[4 * i + 1] = fmaf(g, S[4 * i + 1], kk[i].y * u);
-          S[4 * i + 2] = fmaf(g, S[4 * i + 2], kk[i].z * u); S[4 * i + 3] = fmaf(g, S[4 * i + 3], kk[i].w * u);
-          o0 = fmaf(S[4 * i], qq.x, o0); o1 = fmaf(S[4 * i + 1], qq.y, o1);
-          o2 = fmaf(S[4 * i + 2], qq.z, o2); o3 = fmaf(S[4 * i + 3], qq.w, o3);
+        for (int c = 0; c < C; ++c) {
+          const float dot = column_sum(NA == 4 ? (dk[c][0] + dk[c][1]) + (dk[c][2 % NA] + dk[c][3 % NA]) : dk[c][0] + dk[c][1]);
+          const float rd = column_sum(NA == 4 ? (dq[c][0] + dq[c][1]) + (dq[c][2 % NA] + dq[c][3 % NA]) : dq[c][0] + dq[c][1]);
+          const float u = beta * (x[c] - g * dot);
+          o[c] = fmaf(g, rd, u * kq);
+#pragma unroll
+          for (int i = 0; i < R4; ++i) {
+            S[c][4 * i] = fmaf(g, S[c][4 * i], kk[i].x * u); S[c][4 * i + 1] = fmaf(g, S[c][4 * i + 1], kk[i].y * u);
+            S[c][4 * i + 2] = fmaf(g, S[c][4 * i + 2], kk[i].z * u); S[c][4 * i + 3] = fmaf(g, S[c][4 * i + 3], kk[i].w * u);
+          }
         }
       } else {
+        float oa[C][NA];
 #pragma unroll
-        for (int i = 0; i < R4; ++i) {
-          const float4 ff = k4[4 * i], qq = q4[4 * i];
-          S[4 * i] = fmaf(ff.x, S[4 * i], (1.0f - ff.x) * x); S[4 * i + 1] = fmaf(ff.y, S[4 * i + 1], (1.0f - ff.y) * x);
-          S[4 * i + 2] = fmaf(ff.z, S[4 * i + 2], (1.0f - ff.z) * x); S[4 * i + 3] = fmaf(ff.w, S[4 * i + 3], (1.0f - ff.w) * x);
-          o0 = fmaf(S[4 * i], qq.x, o0); o1 = fmaf(S[4 * i + 1], qq.y, o1);
-          o2 = fmaf(S[4 * i + 2], qq.z, o2); o3 = fmaf(S[4 * i + 3], qq.w, o3);
+        for (int c = 0; c < C; ++c)
+#pragma unroll
+          for (int e = 0; e < NA; ++e) oa[c][e] = 0.f;
+#pragma unroll
+        for (int i = 0; i < R4; ++i) {                // f S + (1 - f) x = x + f (S - x)
+          const float4 ff = k4[PARTS * i], qq = q4[PARTS * i];
+#pragma unroll
+          for (int c = 0; c < C; ++c) {
+            S[c][4 * i] = fmaf(ff.x, S[c][4 * i] - x[c], x[c]); S[c][4 * i + 1] = fmaf(ff.y, S[c][4 * i + 1] - x[c], x[c]);
+            S[c][4 * i + 2] = fmaf(ff.z, S[c][4 * i + 2] - x[c], x[c]); S[c][4 * i + 3] = fmaf(ff.w, S[c][4 * i + 3] - x[c], x[c]);
+            oa[c][0] = fmaf(S[c][4 * i], qq.x, oa[c][0]); oa[c][1] = fmaf(S[c][4 * i + 1], qq.y, oa[c][1]);
+            oa[c][2 % NA] = fmaf(S[c][4 * i + 2], qq.z, oa[c][2 % NA]); oa[c][3 % NA] = fmaf(S[c][4 * i + 3], qq.w, oa[c][3 % NA]);
+          }
         }
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+          o[c] = column_sum(NA == 4 ? (oa[c][0] + oa[c][1]) + (oa[c][2 % NA] + oa[c][3 % NA]) : oa[c][0] + oa[c][1]);
       }
-      float o = (o0 + o1) + (o2 + o3);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      if (live && part == 0) a.y[(int64_t)(start + t0 + t) * H * V + h * V + col] = o;
+      if (part == 0) {
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+          if (col + c < V) a.y[(int64_t)(start + t0 + t) * H * V + h * V + col + c] = o[c];
+      }
     }
     if (more) stage(buf ^ 1);
     __syncthreads();
   }
-  if (live) {
+#pragma unroll
+  for (int c = 0; c < C; ++c)
 #pragma unroll
     for (int i = 0; i < R4; ++i)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int d = 16 * i + 4 * part + e;
-        if (d < D) sp[(int64_t)d * V + col] = S[4 * i + e];
+        const int d = 4 * PARTS * i + 4 * part + e;
+        if (col + c < V && d < D) sp[(int64_t)d * V + col + c] = S[c][4 * i + e];
       }
-  }
 }
 
 template <typename T>
@@ -348,14 +389,29 @@ __global__ void swiglu_scaled_kernel(T* __restrict__ out, int64_t os, const T* _
 
 template <typename T, int MODE>
 int launch_scan(const GlaArgs& a, int64_t num_seqs, cudaStream_t st) {
-  constexpr int cols = kScanThreads / kParts;
-  const dim3 grid((unsigned)((a.V + cols - 1) / cols), (unsigned)a.H, (unsigned)num_seqs);
-#define B2L_GLA(DPV) b2l_launch(gated_linear_scan_kernel<T, DPV, MODE>, grid, dim3(kScanThreads), (size_t)0, st, a)
+  // two columns per thread halve the shared-memory reads per update; one column per thread gives twice the CTAs, which
+  // matters more while the grid does not fill the SMs
+  const auto ctas = [&](int dp, int c) {
+    const int cols = kScanThreads / scan_parts(dp) * c;
+    return (int64_t)((a.V + cols - 1) / cols) * a.H * num_seqs;
+  };
+#define B2L_GLA_C(DPV, CV)                                                                               \
+  do {                                                                                                   \
+    constexpr int cols = kScanThreads / scan_parts(DPV) * CV;                                            \
+    const dim3 grid((unsigned)((a.V + cols - 1) / cols), (unsigned)a.H, (unsigned)num_seqs);             \
+    b2l_launch(gated_linear_scan_kernel<T, DPV, MODE, CV>, grid, dim3(kScanThreads), (size_t)0, st, a);  \
+  } while (0)
+#define B2L_GLA(DPV)                                                                                     \
+  do {                                                                                                   \
+    if (ctas(DPV, 2) >= b2l_num_sms()) B2L_GLA_C(DPV, 2);                                               \
+    else B2L_GLA_C(DPV, 1);                                                                              \
+  } while (0)
   if (a.D <= 16) B2L_GLA(16);
   else if (a.D <= 32) B2L_GLA(32);
   else if (a.D <= 64) B2L_GLA(64);
   else if (a.D <= 128) B2L_GLA(128);
   else B2L_GLA(256);
+#undef B2L_GLA_C
 #undef B2L_GLA
   B2L_LAUNCH_CHECK();
   return B2L_OK;

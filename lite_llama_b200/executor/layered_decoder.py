@@ -359,18 +359,19 @@ def conv_window_attention(li: int, spec: ConvWindowAttentionSpec, w: dict[str, t
     calls = G // per_call if L.head_mix else 1
     width = per_call * Dv if L.head_mix else Dv
     att = torch.empty((b.tokens, calls * H * width), dtype=qkv.dtype, device=qkv.device)
-    for c in range(calls):
-        out = att[:, c * H * width:(c + 1) * H * width]
-        extra = {"v_col0": G * D + c * width, "v_head_stride": 0} if L.head_mix else {}
-        common = (H, G, D, width, L.scale, 0.0)
-        if b.num_portions:
-            sink_attention(out, qkv, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.portion_list, b.num_portions,
-                           b.max_portion, None, *common, window=L.window, **extra)
-        if b.num_singles:
-            keys = b.max_single_ctx + 1
-            splits, per = split_plan(min(keys, L.window) if L.window else keys)
-            sink_attention(out, qkv, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.single_list, b.num_singles,
-                           1, None, *common, num_splits=splits, split_keys=per, window=L.window, **extra)
+    common = (H, G, D, width, L.scale, 0.0)
+    if b.num_portions:
+        for c in range(calls):
+            extra = {"v_col0": G * D + c * width, "v_head_stride": 0} if L.head_mix else {}
+            sink_attention(att[:, c * H * width:(c + 1) * H * width], qkv, pool, ctx.table, b.seq_start, b.seq_ctx,
+                           b.seq_slot, b.portion_list, b.num_portions, b.max_portion, None, *common, window=L.window,
+                           **extra)
+    if b.num_singles:                                # every block of value columns in the same two launches
+        keys = b.max_single_ctx + 1
+        splits, per = split_plan(min(keys, L.window) if L.window else keys)
+        extra = {"v_col0": G * D, "v_head_stride": 0, "v_blocks": calls} if L.head_mix else {}
+        sink_attention(att, qkv, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.single_list, b.num_singles,
+                       1, None, *common, num_splits=splits, split_keys=per, window=L.window, **extra)
     if L.head_mix:
         att = head_mix(att, w["talk"], H, G, per_call, Dv)
     return linear(att, w["left_o"])

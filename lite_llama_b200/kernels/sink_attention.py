@@ -28,21 +28,23 @@ def sink_attention(out: torch.Tensor, q: torch.Tensor, kv_pool: torch.Tensor, ta
                    seq_slot, seq_list: torch.Tensor | None, num_seqs: int, max_q_len: int, sink: torch.Tensor | None,
                    heads: int, kv_heads: int, head_dim: int, v_head_dim: int, scale: float, softcap: float,
                    num_splits: int = 0, split_keys: int = 0, window: int = 0, v_col0: int = -1, block: int = 0,
-                   v_head_stride: int = -1) -> None:
+                   v_head_stride: int = -1, v_blocks: int = 1) -> None:
     """Writes ``out [tokens, heads * v_head_dim]`` for the tokens of the listed sequences.  ``num_splits == 0``: tiled
     kernel (prompt portions); ``> 0``: one new token per sequence, its visible keys cut into ranges of ``split_keys``.
     ``window > 0``: a token at position p sees keys p - window + 1 .. p; ``block > 0`` (no window): keys
     ``floor(p / block) * block .. p`` (a block-diagonal causal mask).  ``v_col0 >= 0``: the values start at that
     column of a pool row instead of after the keys (0: the values are the keys' leading columns).  ``v_head_stride >= 0``:
     kv head g's values start ``g * v_head_stride`` columns further (default ``v_head_dim``; 0: every kv head reads the
-    same ``v_head_dim`` columns, which lets each query head weigh ALL value heads at once as one wide head)."""
+    same ``v_head_dim`` columns, which lets each query head weigh ALL value heads at once as one wide head).
+    ``v_blocks > 1`` (single tokens only): that many neighbouring blocks of ``v_head_dim`` value columns in the same two
+    launches, ``out [tokens, v_blocks * heads * v_head_dim]``."""
     require_cuda(out, q, kv_pool, table)
     L = lib()
-    nbytes = L.b2l_sink_attention_workspace_bytes(num_seqs, heads, v_head_dim, num_splits)
+    nbytes = L.b2l_sink_attention_workspace_bytes(num_seqs, heads * max(1, v_blocks), v_head_dim, num_splits)
     ws = workspace(nbytes, q.device)
     check(L.b2l_sink_attention(out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), kv_pool.data_ptr(),
                                kv_pool.stride(0), table.data_ptr(), table.stride(0), seq_start.data_ptr(),
                                seq_ctx.data_ptr(), seq_slot.data_ptr(), ptr(seq_list), num_seqs, max_q_len, ptr(sink),
                                heads, kv_heads, head_dim, v_head_dim, float(scale), float(softcap or 0.0), int(window),
-                               int(block), int(v_col0), int(v_head_stride), num_splits, split_keys, ptr(ws), nbytes, float_code(q, "q"),
+                               int(block), int(v_col0), int(v_head_stride), int(v_blocks), num_splits, split_keys, ptr(ws), nbytes, float_code(q, "q"),
                                stream_handle()))
