@@ -968,17 +968,15 @@ def gofezen_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) 
         lambda: K.head_mix(wide, talk, H, G, per_call, D), nbytes=T * H * D * (G + 1) * es)
     keys = min(ctx + 1, win)
     splits, per = split_plan(keys)
-    # a step of single tokens runs on the CUDA-core kernel, which takes blocks of up to 256 value columns
-    d_per_call = max(c for c in range(1, G + 1) if G % c == 0 and (c * D <= 256 or c == 1))
-    d_calls, d_width = G // d_per_call, d_per_call * D
+    # a step of single tokens mixes the WEIGHTS: softmax weights per head, then mixed weights times each head's own values
 
     def mixed_decode():
-        K.sink_attention(wide[:batch], proj, pool, tab, d_start, d_ctx, p_slot, None, batch, 1, None, H, G, D, d_width, scale,
-                         0.0, num_splits=splits, split_keys=per, window=win, v_col0=G * D, v_head_stride=0, v_blocks=d_calls)
+        K.mixed_head_attention(out, proj, pool, tab, d_start, d_ctx, p_slot, None, batch, talk, H, G, D, D, scale, 0.0, keys,
+                               window=win)
 
     lkeys = min(ctx + 1, ctx % chunk + 1)
     lsplits, lper = split_plan(min(ctx + 1, chunk))
-    add("window attention over wide values (decode, %d of %d keys seen, %d value blocks in one call)" % (keys, ctx + 1, d_calls),
+    add("window attention, weights mixed across heads (decode, %d of %d keys seen, 2 launches)" % (keys, ctx + 1),
         "block-masked attention (decode, %d keys seen)" % lkeys, mixed_decode, nbytes=batch * keys * kvw * es,
         like_fn=lambda: K.sink_attention(out, proj, pool, tab, d_start, d_ctx, p_slot, None, batch, 1, None, H, G, D, D, scale,
                                          30.0, num_splits=lsplits, split_keys=lper, block=chunk),

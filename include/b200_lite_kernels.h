@@ -388,6 +388,17 @@ int b2l_sink_attention(void* out, int64_t out_row_stride, const void* q, int64_t
                        float scale, float softcap, int window, int block, int v_col0, int v_head_stride,
                        int v_blocks, int num_splits, int split_keys, void* workspace, int64_t workspace_bytes, int dtype,
                        void* stream);
+/* One new token per listed sequence, the heads' softmax weights mixed across heads before the values:
+ * p'_h(j) = sum_g mix[h, g] p_g(j), out_h = sum_j p'_h(j) v_kv(h)(j).  mix [heads, heads] has q's element type.  max_keys
+ * bounds the keys any listed token sees (window, or context + 1); the workspace holds num_seqs * heads * max_keys fp32
+ * weights.  Mask and value-column arguments as in b2l_sink_attention. */
+int64_t b2l_mixed_head_attention_workspace_bytes(int64_t num_seqs, int heads, int max_keys);
+int b2l_mixed_head_attention(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride, const void* kv_pool,
+                             int64_t kv_row_stride, const void* table_i32, int64_t table_row_stride, const void* seq_start,
+                             const void* seq_ctx, const void* seq_slot, const void* seq_list, int64_t num_seqs,
+                             const void* mix, int heads, int kv_heads, int head_dim, int v_head_dim, float scale,
+                             float softcap, int window, int block, int v_col0, int max_keys, void* workspace,
+                             int64_t workspace_bytes, int dtype, void* stream);
 
 /* Parallel-block layer-list models with a depth-weighted residual stack (csrc/parallel_stream.cu).
  * embed_rmsnorm: residual_f32[t] = unit_rms(scale * embed[token[t]]) * (weight_offset + weight) (weight nullable).

@@ -709,6 +709,162 @@ __global__ void __launch_bounds__(64) sink_attention_merge_kernel(T* __restrict_
   }
 }
 
+// ---- one new token per sequence, softmax weights mixed ACROSS heads before they meet the values ---------------------
+// p'_h(j) = sum_g M[h, g] p_g(j);  out_h = sum_j p'_h(j) v_kv(h)(j).  Two launches:
+//   head_weights         CTA = (query head, sequence): thread j scores key j (its pool row read with 16-byte loads, q as
+//                        fp32 in shared memory), softmax in fp32 over the CTA, NORMALISED weights to part [seq][H][chunk]
+//   mixed_weights_values CTA = (query head h, sequence): the mixed weights of head h into shared memory (thread j sums
+//                        over the heads), then warps over the keys and lanes over the value columns (16-byte loads) of
+//                        the head's OWN kv head; the warps' sums meet in shared memory in a fixed order
+// so the values are read once per query head, as in plain attention, and the mix costs H multiply-adds per key.
+constexpr int kMixThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(128) head_weights_kernel(AttnArgs a) {
+  pdl_prologue();
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __shared__ float red[4];
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int D = a.D, Dq = (D + 3) / 4 * 4;
+  float* qs = reinterpret_cast<float*>(smem_raw);                        // [Dq]
+  float* sc = qs + Dq;                                                    // [chunk]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = blockIdx.x, z = blockIdx.y, s = a.seq_list ? a.seq_list[z] : z;
+  const int start = a.seq_start[s], ctx = a.seq_ctx[s];
+  const int64_t slot = a.seq_slot[s];
+  const int g = h / (a.H / a.G);
+  const int lo = max(0, first_visible(a, ctx));
+  const int n = min(ctx + 1 - lo, a.chunk);
+  const T* q = (const T*)a.q + (int64_t)start * a.q_stride + h * D;
+  for (int d = tid; d < D; d += 128) qs[d] = to_f32(q[d]);
+  __syncthreads();
+  const int* trow = a.table + slot * a.table_stride + lo;
+  const T* kv = (const T*)a.kv + g * D;
+  const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
+  const bool vec_ok = (D % VEC == 0) && (a.kv_stride % VEC == 0) && (((uintptr_t)a.kv % 16) == 0);
+  float mx = -INFINITY;
+  for (int j = tid; j < n; j += 128) {
+    const T* kr = kv + (int64_t)trow[j] * a.kv_stride;
+    float dot = 0.f;
+    if (vec_ok) {
+#pragma unroll 4
+      for (int d = 0; d < D; d += VEC) {
+        const uint4 raw = ldg_128(kr + d);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) dot = fmaf(qs[d + c], to_f32(e[c]), dot);
+      }
+    } else {
+      for (int d = 0; d < D; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
+    }
+    float sv = dot * a.scale;
+    if (a.softcap > 0.f) sv = a.softcap * tanhf(sv * inv_cap);
+    sc[j] = sv;
+    mx = fmaxf(mx, sv);
+  }
+  mx = warp_reduce_max(mx);
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  __syncthreads();
+  float sum = 0.f;
+  for (int j = tid; j < n; j += 128) {
+    const float p = expf(sc[j] - mx);
+    sc[j] = p;
+    sum += p;
+  }
+  sum = warp_reduce_sum(sum);
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  sum = (red[0] + red[1]) + (red[2] + red[3]);
+  float* dst = a.part + ((int64_t)z * a.H + h) * a.chunk;
+  for (int j = tid; j < n; j += 128) dst[j] = sc[j] / sum;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kMixThreads) mixed_weights_values_kernel(AttnArgs a, const T* __restrict__ mix) {
+  pdl_prologue();
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  constexpr int VEC = 16 / (int)sizeof(T), kW = kMixThreads / 32;
+  const int Dv = a.Dv, H = a.H;
+  float* pm = reinterpret_cast<float*>(smem_raw);                        // [chunk rounded to 4]
+  float* mrow = pm + (a.chunk + 3) / 4 * 4;                              // [H rounded to 4]
+  float* mrg = mrow + (H + 3) / 4 * 4;                                   // [kW][Dv]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = blockIdx.x, z = blockIdx.y, s = a.seq_list ? a.seq_list[z] : z;
+  const int start = a.seq_start[s], ctx = a.seq_ctx[s];
+  const int64_t slot = a.seq_slot[s];
+  const int g = h / (H / a.G);
+  const int lo = max(0, first_visible(a, ctx));
+  const int n = min(ctx + 1 - lo, a.chunk);
+  for (int i = tid; i < H; i += kMixThreads) mrow[i] = to_f32(mix[(int64_t)h * H + i]);
+  __syncthreads();
+  const float* P = a.part + (int64_t)z * H * a.chunk;
+  for (int j = tid; j < n; j += kMixThreads) {
+    float w = 0.f;
+    for (int gg = 0; gg < H; ++gg) w = fmaf(mrow[gg], P[(int64_t)gg * a.chunk + j], w);
+    pm[j] = w;
+  }
+  __syncthreads();
+  const int* trow = a.table + slot * a.table_stride + lo;
+  const int v_col = a.v_col0 + g * a.v_hstride;
+  const T* vbase = (const T*)a.kv + v_col;
+  const bool vec_ok = (Dv % VEC == 0) && (a.kv_stride % VEC == 0) && (v_col % VEC == 0) && (((uintptr_t)a.kv % 16) == 0);
+  for (int c0 = 0; c0 < Dv; c0 += 32 * VEC) {
+    const int c = c0 + lane * VEC;
+    float acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+    if (vec_ok) {
+      if (c < Dv) {
+#pragma unroll 4
+        for (int j = warp; j < n; j += kW) {
+          const uint4 raw = ldg_128(vbase + (int64_t)trow[j] * a.kv_stride + c);
+          const T* e = reinterpret_cast<const T*>(&raw);
+          const float w = pm[j];
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) acc[i] = fmaf(w, to_f32(e[i]), acc[i]);
+        }
+      }
+    } else {
+      for (int j = warp; j < n; j += kW) {
+        const T* vr = vbase + (int64_t)trow[j] * a.kv_stride;
+        const float w = pm[j];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i)
+          if (c + i < Dv) acc[i] = fmaf(w, to_f32(vr[c + i]), acc[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i)
+      if (c + i < Dv) mrg[warp * Dv + c + i] = acc[i];
+  }
+  __syncthreads();
+  T* o = (T*)a.out + (int64_t)start * a.out_stride + h * Dv;
+  for (int d = tid; d < Dv; d += kMixThreads) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < kW; ++w) v += mrg[w * Dv + d];
+    o[d] = from_f32<T>(v);
+  }
+}
+
+template <typename T>
+int launch_mixed_head_attention(const AttnArgs& a, const void* mix, int64_t num_seqs, cudaStream_t st) {
+  const size_t smem_w = (size_t)((a.D + 3) / 4 * 4 + a.chunk) * sizeof(float);
+  const size_t smem_v = (size_t)((a.chunk + 3) / 4 * 4 + (a.H + 3) / 4 * 4 + (kMixThreads / 32) * a.Dv) * sizeof(float);
+  B2L_REQUIRE((int64_t)smem_w <= b2l_max_smem_optin() && (int64_t)smem_v <= b2l_max_smem_optin(),
+              "mixed_head_attention: %d keys need %lld bytes of shared memory", a.chunk, (long long)(smem_w > smem_v ? smem_w : smem_v));
+  const dim3 grid((unsigned)a.H, (unsigned)num_seqs);
+  static int cache_w[64] = {0}, cache_v[64] = {0};
+  B2L_CUDA_CHECK(b2l_ensure_dynamic_smem(head_weights_kernel<T>, (int)smem_w, cache_w));
+  b2l_launch(head_weights_kernel<T>, grid, dim3(128), smem_w, st, a);
+  B2L_CUDA_CHECK(b2l_ensure_dynamic_smem(mixed_weights_values_kernel<T>, (int)smem_v, cache_v));
+  b2l_launch(mixed_weights_values_kernel<T>, grid, dim3(kMixThreads), smem_v, st, a, (const T*)mix);
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
 __device__ __forceinline__ float block_sum2(float v, float* red) {
   v = warp_reduce_sum(v);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -983,5 +1139,45 @@ extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void*
   const dim3 grid((unsigned)((max_q_len + a.BQ - 1) / a.BQ), (unsigned)(kv_heads * hchunks), (unsigned)num_seqs);
   int rc = B2L_OK;
   B2L_DISPATCH_FLOAT(dtype, "sink_attention", { rc = launch_attention<T>(a, grid, st); });
+  return rc;
+}
+
+extern "C" int64_t b2l_mixed_head_attention_workspace_bytes(int64_t num_seqs, int heads, int max_keys) {
+  return num_seqs * (int64_t)heads * max_keys * (int64_t)sizeof(float);
+}
+
+/* One new token per listed sequence; the heads' softmax weights are mixed by mix [heads, heads] (element type of q,
+ * row h = the weights of head h's sum over the heads) before each head applies them to its own kv head's values.
+ * max_keys: an upper bound of the keys any listed token sees (its window, or its context + 1). */
+extern "C" int b2l_mixed_head_attention(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride,
+                                        const void* kv_pool, int64_t kv_row_stride, const void* table_i32,
+                                        int64_t table_row_stride, const void* seq_start, const void* seq_ctx,
+                                        const void* seq_slot, const void* seq_list, int64_t num_seqs, const void* mix,
+                                        int heads, int kv_heads, int head_dim, int v_head_dim, float scale, float softcap,
+                                        int window, int block, int v_col0, int max_keys, void* workspace,
+                                        int64_t workspace_bytes, int dtype, void* stream) {
+  if (num_seqs <= 0) return B2L_OK;
+  B2L_REQUIRE(out && q && kv_pool && table_i32 && seq_start && seq_ctx && seq_slot && mix, "mixed_head_attention: null pointer");
+  B2L_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && head_dim > 0 && v_head_dim > 0 && max_keys > 0,
+              "mixed_head_attention: bad geometry");
+  const int64_t need = b2l_mixed_head_attention_workspace_bytes(num_seqs, heads, max_keys);
+  B2L_REQUIRE(workspace && workspace_bytes >= need, "mixed_head_attention: workspace too small (%lld < %lld)",
+              (long long)workspace_bytes, (long long)need);
+  AttnArgs a{};
+  a.q = q; a.q_stride = q_row_stride; a.kv = kv_pool; a.kv_stride = kv_row_stride;
+  a.table = (const int*)table_i32; a.table_stride = table_row_stride;
+  a.seq_start = (const int*)seq_start; a.seq_ctx = (const int*)seq_ctx; a.seq_slot = (const int*)seq_slot;
+  a.seq_list = (const int*)seq_list;
+  a.out = out; a.out_stride = out_row_stride; a.part = (float*)workspace;
+  a.H = heads; a.G = kv_heads; a.D = head_dim; a.Dv = v_head_dim;
+  a.chunk = max_keys; a.scale = scale; a.softcap = softcap;
+  a.window = window > 0 ? window : 0;
+  a.block = (window <= 0 && block > 0) ? block : 0;
+  a.v_col0 = v_col0 >= 0 ? v_col0 : kv_heads * head_dim;
+  a.v_hstride = v_head_dim;
+  a.v_blocks = 1;
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = B2L_OK;
+  B2L_DISPATCH_FLOAT(dtype, "mixed_head_attention", { rc = launch_mixed_head_attention<T>(a, mix, num_seqs, st); });
   return rc;
 }

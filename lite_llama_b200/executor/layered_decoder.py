@@ -67,6 +67,8 @@ from ..kernels import (
     rotary_frequencies,
     route_sigmoid_groups,
     sink_attention,
+    mixed_head_attention,
+    MIXED_HEAD_MAX_KEYS,
     softcap_to_f32,
     ssm_scan,
     swiglu_forward,
@@ -345,9 +347,11 @@ def conv_window_attention(li: int, spec: ConvWindowAttentionSpec, w: dict[str, t
                           ctx: StepContext, eps: float) -> torch.Tensor:
     """The attention half of ``window_delta_mixer`` from the fused projection's leading columns [q | k | v]: the short
     convolution (tail per slot), unit-RMS of q and k per head and the cache write, attention under the window, the
-    head mix.  Mixing the heads' softmax weights is linear in the weights, so it is done on OUTPUTS: every query head's
-    weights are applied to the values of every kv head (the value heads of a pool row read side by side as one wide
-    head, ``v_head_stride = 0``), and ``head_mix`` forms ``sum_g M[h, g] * out[g, kv(h)]``."""
+    head mix.  Mixing the heads' softmax weights is linear in the weights.  For prompt portions it is done on OUTPUTS:
+    every query head's weights are applied to the values of every kv head (the value heads of a pool row read side by
+    side as one wide head, ``v_head_stride = 0``), and ``head_mix`` forms ``sum_g M[h, g] * out[g, kv(h)]``, so the
+    tiled softmax kernels stay as they are.  For single tokens the normalised weights of a token are small
+    (``heads x keys``): ``mixed_head_attention`` writes them, mixes them and reads each head's own values once."""
     b, L = ctx.batch, spec
     H, G, D, Dv = L.heads, L.kv_heads, L.head_dim, L.v_head_dim
     pool = ctx.kv_buffer[li]
@@ -355,25 +359,41 @@ def conv_window_attention(li: int, spec: ConvWindowAttentionSpec, w: dict[str, t
                            b.seq_start, b.seq_ctx, b.seq_slot, activation=False)
     ones = w["ones"] if L.qk_unit_rms else None
     head_norm_rope_prepare(qkv, pool, b.kv_rows, None, ones, ones, H, G, D, Dv, 0, eps)
-    per_call = wide_value_heads(L, qkv.dtype != torch.float32 and b.num_portions > 0) if L.head_mix else 0
-    calls = G // per_call if L.head_mix else 1
-    width = per_call * Dv if L.head_mix else Dv
-    att = torch.empty((b.tokens, calls * H * width), dtype=qkv.dtype, device=qkv.device)
-    common = (H, G, D, width, L.scale, 0.0)
-    if b.num_portions:
-        for c in range(calls):
-            extra = {"v_col0": G * D + c * width, "v_head_stride": 0} if L.head_mix else {}
-            sink_attention(att[:, c * H * width:(c + 1) * H * width], qkv, pool, ctx.table, b.seq_start, b.seq_ctx,
+    if not L.head_mix:
+        att = torch.empty((b.tokens, H * Dv), dtype=qkv.dtype, device=qkv.device)
+        common = (H, G, D, Dv, L.scale, 0.0)
+        if b.num_portions:
+            sink_attention(att, qkv, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.portion_list, b.num_portions,
+                           b.max_portion, None, *common, window=L.window)
+        if b.num_singles:
+            keys = b.max_single_ctx + 1
+            splits, per = split_plan(min(keys, L.window) if L.window else keys)
+            sink_attention(att, qkv, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.single_list, b.num_singles,
+                           1, None, *common, num_splits=splits, split_keys=per, window=L.window)
+        return linear(att, w["left_o"])
+    keys = min(b.max_single_ctx + 1, L.window) if L.window else b.max_single_ctx + 1
+    direct = b.num_singles > 0 and keys <= MIXED_HEAD_MAX_KEYS     # single tokens: the WEIGHTS are mixed, two launches
+    att = None
+    if b.num_portions or (b.num_singles and not direct):
+        per_call = wide_value_heads(L, qkv.dtype != torch.float32 and b.num_portions > 0)
+        calls, width = G // per_call, per_call * Dv
+        wide = torch.empty((b.tokens, calls * H * width), dtype=qkv.dtype, device=qkv.device)
+        common = (H, G, D, width, L.scale, 0.0)
+        for c in range(calls if b.num_portions else 0):
+            sink_attention(wide[:, c * H * width:(c + 1) * H * width], qkv, pool, ctx.table, b.seq_start, b.seq_ctx,
                            b.seq_slot, b.portion_list, b.num_portions, b.max_portion, None, *common, window=L.window,
-                           **extra)
-    if b.num_singles:                                # every block of value columns in the same two launches
-        keys = b.max_single_ctx + 1
-        splits, per = split_plan(min(keys, L.window) if L.window else keys)
-        extra = {"v_col0": G * D, "v_head_stride": 0, "v_blocks": calls} if L.head_mix else {}
-        sink_attention(att, qkv, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.single_list, b.num_singles,
-                       1, None, *common, num_splits=splits, split_keys=per, window=L.window, **extra)
-    if L.head_mix:
-        att = head_mix(att, w["talk"], H, G, per_call, Dv)
+                           v_col0=G * D + c * width, v_head_stride=0)
+        if b.num_singles and not direct:                 # every block of value columns in the same two launches
+            splits, per = split_plan(keys)
+            sink_attention(wide, qkv, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.single_list, b.num_singles,
+                           1, None, *common, num_splits=splits, split_keys=per, window=L.window, v_col0=G * D,
+                           v_head_stride=0, v_blocks=calls)
+        att = head_mix(wide, w["talk"], H, G, per_call, Dv)      # rows of tokens no call wrote are overwritten below
+    if direct:
+        if att is None:
+            att = torch.empty((b.tokens, H * Dv), dtype=qkv.dtype, device=qkv.device)
+        mixed_head_attention(att, qkv, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.single_list, b.num_singles,
+                             w["talk"], H, G, D, Dv, L.scale, 0.0, keys, window=L.window)
     return linear(att, w["left_o"])
 
 

@@ -14,7 +14,7 @@ from .linear import linear, linear_simt
 from .parallel_stream import branch_sum_residual, depth_mix_norms, embed_rmsnorm, gelu_mul_gather
 from .rotary_heads import head_norm_rope_prepare, rope_table_freqs, rotary_frequencies
 from .residual_stream import embed_positions, gelu, post_norm_residual, relu_squared, rmsnorm_from_f32, softcap_to_f32
-from .sink_attention import attn_prepare, sink_attention
+from .sink_attention import MIXED_HEAD_MAX_KEYS, attn_prepare, mixed_head_attention, sink_attention
 from .ssm import causal_conv_silu, decay_attention, gated_group_norm, gated_scan, norm_sigmoid_gate, ssm_scan
 from .rope_emb import rope_emb_forward, rope_emb_inplace, rope_kv_write
 from .sampling import argmax_rows
@@ -50,6 +50,8 @@ __all__ = [
     "relu_squared",
     "attn_prepare",
     "sink_attention",
+    "mixed_head_attention",
+    "MIXED_HEAD_MAX_KEYS",
     "causal_conv_silu",
     "ssm_scan",
     "gated_group_norm",

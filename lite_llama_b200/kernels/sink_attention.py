@@ -48,3 +48,29 @@ def sink_attention(out: torch.Tensor, q: torch.Tensor, kv_pool: torch.Tensor, ta
                                heads, kv_heads, head_dim, v_head_dim, float(scale), float(softcap or 0.0), int(window),
                                int(block), int(v_col0), int(v_head_stride), int(v_blocks), num_splits, split_keys, ptr(ws), nbytes, float_code(q, "q"),
                                stream_handle()))
+
+
+MIXED_HEAD_MAX_KEYS = 32768      # the weights of one head and sequence stay in a CTA's shared memory
+
+
+@torch.no_grad()
+def mixed_head_attention(out: torch.Tensor, q: torch.Tensor, kv_pool: torch.Tensor, table: torch.Tensor, seq_start,
+                         seq_ctx, seq_slot, seq_list: torch.Tensor | None, num_seqs: int, mix: torch.Tensor, heads: int,
+                         kv_heads: int, head_dim: int, v_head_dim: int, scale: float, softcap: float, max_keys: int,
+                         window: int = 0, block: int = 0, v_col0: int = -1) -> None:
+    """One new token per listed sequence: softmax over its visible keys per head, the heads' weights mixed by
+    ``mix [heads, heads]`` (``p'_h = sum_g mix[h, g] p_g``), each head's mixed weights applied to its own kv head's
+    values; writes ``out [tokens, heads * v_head_dim]`` rows of those tokens.  ``max_keys`` bounds the keys any of the
+    tokens sees (at most ``MIXED_HEAD_MAX_KEYS``)."""
+    require_cuda(out, q, kv_pool, table, mix)
+    if mix.dtype != q.dtype or mix.numel() != heads * heads or not mix.is_contiguous() or not 0 < max_keys <= MIXED_HEAD_MAX_KEYS:
+        raise ValueError("mixed_head_attention: bad mixing matrix or key bound")
+    L = lib()
+    nbytes = L.b2l_mixed_head_attention_workspace_bytes(num_seqs, heads, max_keys)
+    ws = workspace(nbytes, q.device)
+    check(L.b2l_mixed_head_attention(out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), kv_pool.data_ptr(),
+                                     kv_pool.stride(0), table.data_ptr(), table.stride(0), seq_start.data_ptr(),
+                                     seq_ctx.data_ptr(), seq_slot.data_ptr(), ptr(seq_list), num_seqs, mix.data_ptr(),
+                                     heads, kv_heads, head_dim, v_head_dim, float(scale), float(softcap or 0.0),
+                                     int(window), int(block), int(v_col0), int(max_keys), ptr(ws), nbytes,
+                                     float_code(q, "q"), stream_handle()))

@@ -195,6 +195,29 @@ def test_convolved_window_attention_with_mixed_heads_in_portions_and_single_toke
         _close(got[i], refs[i], tol)
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 3e-2)])
+@pytest.mark.parametrize("geom", [dict(heads=8, kv_heads=4, dim=32, vdim=64, size=33, conv=2),
+                                  dict(heads=4, kv_heads=2, dim=16, vdim=136, size=50, conv=1),    # fp32 lanes pass twice
+                                  dict(heads=5, kv_heads=1, dim=7, vdim=3, size=300, conv=3)])
+def test_single_tokens_with_mixed_outputs_instead_of_mixed_weights(monkeypatch, dtype, tol, geom):
+    """Steps of single tokens mix the heads' WEIGHTS (two launches); a window too long for that falls back to weighing
+    every value head and mixing the outputs.  Both are the same sum: the fallback is forced here."""
+    import lite_llama_b200.executor.layered_decoder as LD
+    m = O.left_entry(scale=2.0 / geom["dim"] ** 0.5, **geom)
+    cols = m["heads"] * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"])
+    g = torch.Generator().manual_seed(geom["vdim"])
+    xs = [torch.randn(L, cols, generator=g).to(dtype).float() for L in (130, 50)]
+    talk = (0.4 * torch.randn(m["heads"], m["heads"], generator=g) + torch.eye(m["heads"])).to(dtype).float()
+    cw = (0.6 * torch.randn(cols, m["conv"], generator=g)).to(dtype).float()
+    refs = [O.window_attention(O.f64(x), m, _attention_weights(m, cols, talk, cw), 1e-5) for x in xs]
+    direct = _attention_case(m, PLAN, dtype, xs, talk, cw)
+    monkeypatch.setattr(LD, "MIXED_HEAD_MAX_KEYS", 0)
+    fallback = _attention_case(m, PLAN, dtype, xs, talk, cw)
+    for i in (0, 1):
+        _close(direct[i], refs[i], tol)
+        _close(fallback[i], refs[i], tol)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("new", [1, 2, 40])
 @pytest.mark.parametrize("size", [1, 7, 64, 65, 136, 200])
