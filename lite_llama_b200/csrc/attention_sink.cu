@@ -746,13 +746,19 @@ __global__ void __launch_bounds__(128) head_weights_kernel(AttnArgs a) {
   for (int j = tid; j < n; j += 128) {
     const T* kr = kv + (int64_t)trow[j] * a.kv_stride;
     float dot = 0.f;
-    if (vec_ok) {
-#pragma unroll 4
-      for (int d = 0; d < D; d += VEC) {
-        const uint4 raw = ldg_128(kr + d);
-        const T* e = reinterpret_cast<const T*>(&raw);
+    if (vec_ok) {                                  // 8 loads of the row in flight before the first product
+      for (int d0 = 0; d0 < D; d0 += 8 * VEC) {
+        uint4 raw[8];
 #pragma unroll
-        for (int c = 0; c < VEC; ++c) dot = fmaf(qs[d + c], to_f32(e[c]), dot);
+        for (int u = 0; u < 8; ++u) raw[u] = d0 + u * VEC < D ? ldg_128(kr + d0 + u * VEC) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const T* e = reinterpret_cast<const T*>(&raw[u]);
+          if (d0 + u * VEC < D) {
+#pragma unroll
+            for (int c = 0; c < VEC; ++c) dot = fmaf(qs[d0 + u * VEC + c], to_f32(e[c]), dot);
+          }
+        }
       }
     } else {
       for (int d = 0; d < D; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
@@ -781,16 +787,27 @@ __global__ void __launch_bounds__(128) head_weights_kernel(AttnArgs a) {
   for (int j = tid; j < n; j += 128) dst[j] = sc[j] / sum;
 }
 
+// lanes that share one key in mixed_weights_values (a power of two: enough 16-byte groups to cover the value head, at
+// most a warp) and the floats of its merge buffer: one row of Dv sums per group of lanes
+__host__ __device__ inline int mix_lanes_per_key(int Dv, int vec) {
+  const int groups = (Dv + vec - 1) / vec;
+  int l = 1;
+  while (l < groups && l < 32) l *= 2;
+  return l;
+}
+__host__ __device__ inline int mix_merge_floats(int Dv, int vec) { return kMixThreads / mix_lanes_per_key(Dv, vec) * Dv; }
+
 template <typename T>
 __global__ void __launch_bounds__(kMixThreads) mixed_weights_values_kernel(AttnArgs a, const T* __restrict__ mix) {
   pdl_prologue();
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  constexpr int VEC = 16 / (int)sizeof(T), kW = kMixThreads / 32;
-  const int Dv = a.Dv, H = a.H;
-  float* pm = reinterpret_cast<float*>(smem_raw);                        // [chunk rounded to 4]
-  float* mrow = pm + (a.chunk + 3) / 4 * 4;                              // [H rounded to 4]
-  float* mrg = mrow + (H + 3) / 4 * 4;                                   // [kW][Dv]
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int Dv = a.Dv, H = a.H, chunk4 = (a.chunk + 3) / 4 * 4;
+  float* pm = reinterpret_cast<float*>(smem_raw);                        // [chunk4] mixed weights
+  int* rows = reinterpret_cast<int*>(pm + chunk4);                       // [chunk4] pool rows of the keys
+  float* mrow = reinterpret_cast<float*>(rows + chunk4);                 // [H rounded to 4]
+  float* mrg = mrow + (H + 3) / 4 * 4;                                   // [groups of lanes][Dv]
+  const int tid = threadIdx.x;
   const int h = blockIdx.x, z = blockIdx.y, s = a.seq_list ? a.seq_list[z] : z;
   const int start = a.seq_start[s], ctx = a.seq_ctx[s];
   const int64_t slot = a.seq_slot[s];
@@ -800,26 +817,29 @@ __global__ void __launch_bounds__(kMixThreads) mixed_weights_values_kernel(AttnA
   for (int i = tid; i < H; i += kMixThreads) mrow[i] = to_f32(mix[(int64_t)h * H + i]);
   __syncthreads();
   const float* P = a.part + (int64_t)z * H * a.chunk;
+  const int* trow = a.table + slot * a.table_stride + lo;
   for (int j = tid; j < n; j += kMixThreads) {
+    rows[j] = trow[j];
     float w = 0.f;
     for (int gg = 0; gg < H; ++gg) w = fmaf(mrow[gg], P[(int64_t)gg * a.chunk + j], w);
     pm[j] = w;
   }
   __syncthreads();
-  const int* trow = a.table + slot * a.table_stride + lo;
   const int v_col = a.v_col0 + g * a.v_hstride;
   const T* vbase = (const T*)a.kv + v_col;
   const bool vec_ok = (Dv % VEC == 0) && (a.kv_stride % VEC == 0) && (v_col % VEC == 0) && (((uintptr_t)a.kv % 16) == 0);
-  for (int c0 = 0; c0 < Dv; c0 += 32 * VEC) {
-    const int c = c0 + lane * VEC;
+  const int lpk = mix_lanes_per_key(Dv, VEC), groups = kMixThreads / lpk;
+  const int gi = tid / lpk, l = tid - gi * lpk;                          // group of lanes (one key at a time), lane in it
+  for (int c0 = 0; c0 < Dv; c0 += lpk * VEC) {
+    const int c = c0 + l * VEC;
     float acc[VEC];
 #pragma unroll
     for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
     if (vec_ok) {
       if (c < Dv) {
-#pragma unroll 4
-        for (int j = warp; j < n; j += kW) {
-          const uint4 raw = ldg_128(vbase + (int64_t)trow[j] * a.kv_stride + c);
+#pragma unroll 8
+        for (int j = gi; j < n; j += groups) {
+          const uint4 raw = ldg_128(vbase + (int64_t)rows[j] * a.kv_stride + c);
           const T* e = reinterpret_cast<const T*>(&raw);
           const float w = pm[j];
 #pragma unroll
@@ -827,8 +847,8 @@ __global__ void __launch_bounds__(kMixThreads) mixed_weights_values_kernel(AttnA
         }
       }
     } else {
-      for (int j = warp; j < n; j += kW) {
-        const T* vr = vbase + (int64_t)trow[j] * a.kv_stride;
+      for (int j = gi; j < n; j += groups) {
+        const T* vr = vbase + (int64_t)rows[j] * a.kv_stride;
         const float w = pm[j];
 #pragma unroll
         for (int i = 0; i < VEC; ++i)
@@ -837,14 +857,13 @@ __global__ void __launch_bounds__(kMixThreads) mixed_weights_values_kernel(AttnA
     }
 #pragma unroll
     for (int i = 0; i < VEC; ++i)
-      if (c + i < Dv) mrg[warp * Dv + c + i] = acc[i];
+      if (c + i < Dv) mrg[gi * Dv + c + i] = acc[i];
   }
   __syncthreads();
   T* o = (T*)a.out + (int64_t)start * a.out_stride + h * Dv;
   for (int d = tid; d < Dv; d += kMixThreads) {
     float v = 0.f;
-#pragma unroll
-    for (int w = 0; w < kW; ++w) v += mrg[w * Dv + d];
+    for (int w = 0; w < groups; ++w) v += mrg[w * Dv + d];             // a fixed order: the same sum in every batch
     o[d] = from_f32<T>(v);
   }
 }
@@ -852,7 +871,8 @@ __global__ void __launch_bounds__(kMixThreads) mixed_weights_values_kernel(AttnA
 template <typename T>
 int launch_mixed_head_attention(const AttnArgs& a, const void* mix, int64_t num_seqs, cudaStream_t st) {
   const size_t smem_w = (size_t)((a.D + 3) / 4 * 4 + a.chunk) * sizeof(float);
-  const size_t smem_v = (size_t)((a.chunk + 3) / 4 * 4 + (a.H + 3) / 4 * 4 + (kMixThreads / 32) * a.Dv) * sizeof(float);
+  const size_t smem_v = (size_t)(2 * ((a.chunk + 3) / 4 * 4) + (a.H + 3) / 4 * 4 +
+                                 mix_merge_floats(a.Dv, 16 / (int)sizeof(T))) * sizeof(float);
   B2L_REQUIRE((int64_t)smem_w <= b2l_max_smem_optin() && (int64_t)smem_v <= b2l_max_smem_optin(),
               "mixed_head_attention: %d keys need %lld bytes of shared memory", a.chunk, (long long)(smem_w > smem_v ? smem_w : smem_v));
   const dim3 grid((unsigned)a.H, (unsigned)num_seqs);
