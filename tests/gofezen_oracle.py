@@ -217,7 +217,7 @@ def hgrn2_layer(heads=2, dim=4, vdim=6, mlp="dense") -> dict:
             "mlp": dense_mlp() if mlp == "dense" else mlp}
 
 
-def pair_layer(left=None, right=None, left_scale=0.6, right_scale=0.9, mlp="moe") -> dict:
+def pair_layer(left=None, right=None, left_scale=0.7, right_scale=1.2, mlp="moe") -> dict:
     return {"type": "parallel", "mixer": {"left": left or left_entry(), "right": right or right_entry(),
                                           "left_scale": left_scale, "right_scale": right_scale},
             "mlp": moe_mlp() if mlp == "moe" else mlp}

@@ -99,7 +99,7 @@ def test_value_heads_read_side_by_side_fit_the_attention_kernels():
     spec = lambda kv, vdim, dim=64: ConvWindowAttentionSpec(heads=kv * 2, kv_heads=kv, head_dim=dim, v_head_dim=vdim, scale=1.0)
     assert wide_value_heads(spec(2, 64), True) == 2 and wide_value_heads(spec(4, 64), True) == 2
     assert wide_value_heads(spec(4, 64), False) == 4 and wide_value_heads(spec(3, 64), True) == 1
-    assert wide_value_heads(spec(8, 16), True) == 8 and wide_value_heads(spec(2, 136), True) == 1
+    assert wide_value_heads(spec(8, 16), True) == 8 and wide_value_heads(spec(2, 144), True) == 1
     assert wide_value_heads(spec(6, 40, dim=20), True) == 6           # odd head size: the CUDA-core kernel's 256 columns
 
 

@@ -55,7 +55,7 @@ PLAN = [[(0, 0, 40), (1, 0, 9)], [(1, 9, 11), (0, 40, 110)], [(0, 110, 111)], [(
 
 # ------------------------------------------------------------------------------------------- mechanisms alone #
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 3e-2)])
-@pytest.mark.parametrize("heads,dim,vdim", [(2, 8, 6), (4, 32, 64), (1, 5, 1), (3, 24, 40), (2, 80, 72), (1, 200, 16),
+@pytest.mark.parametrize("heads,dim,vdim", [(2, 8, 6), (4, 32, 96), (1, 5, 1), (3, 24, 40), (2, 80, 72), (1, 200, 16),
                                             (2, 128, 130)])
 def test_forget_gate_memory_over_portions_and_single_tokens(dtype, tol, heads, dim, vdim):
     from lite_llama_b200.kernels import gated_linear_scan, head_norm_gate
@@ -88,7 +88,7 @@ def test_forget_gate_memory_over_portions_and_single_tokens(dtype, tol, heads, d
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-5), (torch.bfloat16, 4e-2)])
-@pytest.mark.parametrize("heads,qk,dim,vdim,taps", [(2, 1, 8, 6, 2), (4, 2, 32, 32, 4), (1, 1, 5, 1, 1), (3, 3, 24, 40, 3),
+@pytest.mark.parametrize("heads,qk,dim,vdim,taps", [(2, 1, 8, 6, 2), (4, 2, 32, 48, 4), (1, 1, 5, 1, 1), (3, 3, 24, 40, 3),
                                                     (6, 2, 64, 72, 5), (1, 1, 200, 16, 2), (2, 2, 128, 128, 4)])
 def test_delta_rule_with_its_convolution_gates_and_output_norm(dtype, tol, heads, qk, dim, vdim, taps):
     from lite_llama_b200.kernels import causal_conv_silu, gated_linear_scan, head_norm_gate
@@ -177,9 +177,9 @@ def _attention_weights(m, cols, talk, conv_w):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 3e-2)])
 @pytest.mark.parametrize("geom", [dict(heads=3, kv_heads=1, dim=6, vdim=5, size=9, conv=3),
-                                  dict(heads=4, kv_heads=2, dim=64, vdim=64, size=70, conv=3),
+                                  dict(heads=4, kv_heads=2, dim=64, vdim=32, size=70, conv=3),
                                   dict(heads=8, kv_heads=4, dim=32, vdim=64, size=33, conv=2),     # two calls of two value heads
-                                  dict(heads=2, kv_heads=2, dim=16, vdim=136, size=128, conv=4),   # one value head per call
+                                  dict(heads=2, kv_heads=2, dim=16, vdim=144, size=128, conv=4),   # one value head per call
                                   dict(heads=6, kv_heads=1, dim=8, vdim=8, size=1, conv=1),
                                   dict(heads=2, kv_heads=1, dim=40, vdim=24, size=1000, conv=5)])
 def test_convolved_window_attention_with_mixed_heads_in_portions_and_single_tokens(dtype, tol, geom):
@@ -197,7 +197,7 @@ def test_convolved_window_attention_with_mixed_heads_in_portions_and_single_toke
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 3e-2)])
 @pytest.mark.parametrize("geom", [dict(heads=8, kv_heads=4, dim=32, vdim=64, size=33, conv=2),
-                                  dict(heads=4, kv_heads=2, dim=16, vdim=136, size=50, conv=1),    # fp32 lanes pass twice
+                                  dict(heads=4, kv_heads=2, dim=16, vdim=144, size=50, conv=1),    # fp32 lanes pass twice
                                   dict(heads=5, kv_heads=1, dim=7, vdim=3, size=300, conv=3)])
 def test_single_tokens_with_mixed_outputs_instead_of_mixed_weights(monkeypatch, dtype, tol, geom):
     """Steps of single tokens mix the heads' WEIGHTS (two launches); a window too long for that falls back to weighing
@@ -220,7 +220,7 @@ def test_single_tokens_with_mixed_outputs_instead_of_mixed_weights(monkeypatch, 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("new", [1, 2, 40])
-@pytest.mark.parametrize("size", [1, 7, 64, 65, 136, 200])
+@pytest.mark.parametrize("size", [1, 7, 64, 65, 130, 200])
 def test_a_key_at_the_window_edge_is_seen_and_the_one_before_it_is_not(dtype, new, size):
     """One key is made to stand out for the last query (aligned with it, everything else orthogonal noise): at distance
     ``size - 1`` its value fills the output, at distance ``size`` it leaves no trace.  The last token comes in a
@@ -270,7 +270,7 @@ def _moe_weights(cfg_mlp, width, seed, dtype):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 4e-2)])
-@pytest.mark.parametrize("experts,top,ff,shared,width", [(5, 2, 6, 7, 24), (12, 1, 96, 128, 256), (1, 1, 8, 0, 16),
+@pytest.mark.parametrize("experts,top,ff,shared,width", [(5, 2, 6, 7, 24), (10, 1, 80, 112, 192), (1, 1, 8, 0, 16),
                                                          (7, 7, 5, 3, 20), (16, 4, 64, 64, 128)])
 def test_routed_gated_experts_weigh_their_input_with_unnormalised_scores(dtype, tol, experts, top, ff, shared, width):
     from lite_llama_b200.executor.layered_decoder import _gofezen_mlp, map_gofezen_weights, moe_feed_forward, parse_gofezen_config
@@ -303,16 +303,16 @@ def test_scaled_branches_join_the_residual_and_hand_out_the_next_norm(dtype, tol
     a, b, c = (torch.randn(T, n + 8).to(dtype) for _ in range(3))
     wn = (1 + 0.3 * torch.randn(n)).to(dtype)
     r = r0.clone().to(DEV)
-    act = branch_sum_residual(r, a.to(DEV)[:, :n], None, b.to(DEV)[:, 4:n + 4], None, c.to(DEV)[:, 8:], eps, 0.6,
-                              want_act=False, scale_b=0.9, next_weight=wn.to(DEV))
-    ref = O.f64(r0) + 0.6 * O.f64(a)[:, :n] + 0.9 * O.f64(b)[:, 4:n + 4] + O.f64(c)[:, 8:]
+    act = branch_sum_residual(r, a.to(DEV)[:, :n], None, b.to(DEV)[:, 4:n + 4], None, c.to(DEV)[:, 8:], eps, 0.7,
+                              want_act=False, scale_b=1.3, next_weight=wn.to(DEV))
+    ref = O.f64(r0) + 0.7 * O.f64(a)[:, :n] + 1.3 * O.f64(b)[:, 4:n + 4] + O.f64(c)[:, 8:]
     _close(r, ref, 3e-6)
     _close(act, np.stack([O.unit_rms(x, eps) for x in ref]) * O.f64(wn), tol)
     r = r0.clone().to(DEV)
     assert branch_sum_residual(r, a.to(DEV)[:, :n], None, None, None, None, eps, 1.0, want_act=False) is None
     _close(r, O.f64(r0) + O.f64(a)[:, :n], 3e-6)
     z = torch.randn(5, 33).to(dtype)
-    _close(softcap_to_f32(z.to(DEV), 15.0, 0.5), 15.0 * np.tanh(0.5 * O.f64(z) / 15.0), 3e-6)
+    _close(softcap_to_f32(z.to(DEV), 12.0, 0.75), 12.0 * np.tanh(0.75 * O.f64(z) / 12.0), 3e-6)
     _close(softcap_to_f32(z.to(DEV), 0.0, 0.25), 0.25 * O.f64(z), 3e-6)
 
 
@@ -328,7 +328,7 @@ def _small():
 def _aligned():
     # sizes in steps of 8: the tensor-core tiles in bf16; a window longer than a 64-key tile, one of exactly two tiles
     a = O.left_entry(heads=6, kv_heads=1, dim=32, vdim=24, size=70, conv=3, scale=0.25)
-    b = O.left_entry(heads=4, kv_heads=2, dim=64, vdim=64, size=128, conv=4, scale=0.125)
+    b = O.left_entry(heads=4, kv_heads=2, dim=64, vdim=64, size=128, conv=4, scale=0.11)
     return O.make_config([O.pair_layer(a, O.right_entry(heads=4, kv_heads=2, dim=32, vdim=16, conv=4), mlp=O.moe_mlp(8, 2, 32, 48)),
                           O.hgrn2_layer(heads=2, dim=32, vdim=64, mlp=O.dense_mlp(96)),
                           O.hgrn2_layer(heads=4, dim=16, vdim=16, mlp=O.moe_mlp(6, 1, 24, 16)),
@@ -582,8 +582,8 @@ def _random_config(rng, odd):
         kv = rng.choice([1, 2, 3, 4])
         return O.left_entry(heads=kv * rng.choice([1, 2, 3]), kv_heads=kv, dim=dim,
                             vdim=rng.choice([3, 10, 33] if odd else [8, 24, 64, 80]),
-                            size=rng.choice([1, 2, 5, 16, 33, 64, 65, 100, 128, 136, 200, 1000]), conv=rng.choice([1, 2, 3, 4]),
-                            scale=rng.choice([0.125, 0.5, 1.0]))
+                            size=rng.choice([1, 2, 5, 16, 33, 64, 65, 100, 128, 130, 200, 1000]), conv=rng.choice([1, 2, 3, 4]),
+                            scale=rng.choice([0.1, 0.5, 1.0]))
 
     def right():
         qk = rng.choice([1, 2])
@@ -603,13 +603,13 @@ def _random_config(rng, odd):
     layers = []
     for _ in range(rng.randint(2, 6)):
         if rng.random() < 0.5:
-            layers.append(O.pair_layer(left(), right(), rng.choice([0.3, 0.6, 1.0]), rng.choice([0.9, 1.0, 1.5]), ff()))
+            layers.append(O.pair_layer(left(), right(), rng.choice([0.3, 0.7, 1.0]), rng.choice([0.8, 1.0, 1.5]), ff()))
         else:
             layers.append(O.hgrn2_layer(rng.choice([1, 2, 4]), rng.choice([5, 31] if odd else [8, 32, 48]),
                                         rng.choice([3, 17] if odd else [8, 64]), ff()))
-    return O.make_config(layers, width=rng.choice([50, 92, 37, 129] if odd else [16, 40, 72, 136, 200]),
+    return O.make_config(layers, width=rng.choice([50, 92, 37, 129] if odd else [16, 40, 72, 144, 200]),
                          vocab=rng.choice([33, 1001] if odd else [17, 64, 300]), eps=rng.choice([1e-5, 1e-6, 1e-3]),
-                         embed_scale=rng.choice([1.0, 4.0, 16.0]), logit_scale=rng.choice([0.5, 1.0, 2.0]),
+                         embed_scale=rng.choice([1.0, 4.0, 8.0]), logit_scale=rng.choice([0.75, 1.0, 2.0]),
                          softcap=rng.choice([0.0, 10.0, 30.0]), max_positions=256)
 
 
