@@ -10,8 +10,9 @@
 //                          (the read-out sees the current token's write)
 //
 // 4 to 16 neighbouring lanes share one value column of one head and hold at most 16 of its D memory entries each in
-// registers, so a contraction over D (S^T k, S^T q) is a sum inside a thread plus a few shuffles, and a thread needs
-// about 64 registers: 32 warps are resident on an SM and hide the token-to-token dependency.  The delta rule's two
+// registers, so a contraction over D (S^T k, S^T q) is a sum inside a thread plus a few shuffles, nothing spills
+// (87 to 128 registers with the prefetched rows: two CTAs of 8 warps per SM), and several times the threads work on a
+// head than with one thread per value column.  The delta rule's two
 // contractions both read the memory before the token's write (S'^T q = g S^T q + u (k . q)), so they run side by side.
 // A CTA = (256 / lanes value columns, head, sequence) stages 16 tokens at a time in one of two buffers: the token's
 // gates, unit norms and scalars are evaluated in fp32 by the warps in parallel and left in shared memory with the
@@ -53,8 +54,8 @@ struct GlaArgs {
 };
 
 constexpr int kScanThreads = 256;
-// lanes that share one value column (neighbouring lanes): each holds at most 16 memory rows, so a thread stays near 64
-// registers and four CTAs (32 warps) are resident on an SM to hide the token-to-token dependency
+// lanes that share one value column (neighbouring lanes): each holds at most 16 memory rows, so nothing spills and a
+// head's update is spread over 4 to 16 times the threads of one-thread-per-column
 constexpr int scan_parts(int dp) { return dp <= 64 ? 4 : dp / 16; }
 
 template <typename T, int DP, int MODE, int C>
