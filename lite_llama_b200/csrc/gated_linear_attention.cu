@@ -356,6 +356,42 @@ __global__ void head_mix_vec_kernel(T* __restrict__ out, const T* __restrict__ w
   }
 }
 
+// the same with one thread per (token, kv head, 4 value columns) forming ALL the PER output heads of that kv head: a
+// wide element is loaded once instead of once per output head; every output is the same g-ascending sum as above
+template <typename T, int PER>
+__global__ void head_mix_group_kernel(T* __restrict__ out, const T* __restrict__ wide, int64_t wide_stride,
+                                      const T* __restrict__ mix, int heads, int kv_heads, int per_call, int Dv,
+                                      int64_t total4) {
+  pdl_prologue();
+  const int q4 = Dv / 4;
+  const int64_t call_stride = (int64_t)heads * per_call * Dv, g_stride = (int64_t)per_call * Dv;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total4; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % q4) * 4;
+    const int c = (int)((idx / q4) % kv_heads);
+    const int64_t t = idx / ((int64_t)q4 * kv_heads);
+    const T* src = wide + t * wide_stride + (c / per_call) * call_stride + (int64_t)(c % per_call) * Dv + i;
+    const T* mrow = mix + (int64_t)c * PER * heads;
+    float acc[PER][4];
+#pragma unroll
+    for (int r = 0; r < PER; ++r)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[r][e] = 0.f;
+#pragma unroll 4
+    for (int g = 0; g < heads; ++g) {
+      float v[4];
+      row_load4(src + g * g_stride, v);
+#pragma unroll
+      for (int r = 0; r < PER; ++r) {
+        const float m = to_f32(mrow[r * heads + g]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[r][e] = fmaf(m, v[e], acc[r][e]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < PER; ++r) row_store4(out + (t * heads + c * PER + r) * (int64_t)Dv + i, acc[r]);
+  }
+}
+
 template <typename T>
 __global__ void swiglu_scaled_vec_kernel(T* __restrict__ out, int64_t os, const T* __restrict__ gate, int64_t gs,
                                          const T* __restrict__ up, int64_t us, const float* __restrict__ in_scale,
@@ -478,17 +514,27 @@ extern "C" int b2l_head_mix(void* out, const void* wide, int64_t wide_row_stride
   if (rows <= 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t total = rows * heads * vdim;
+#define B2L_MIX_GROUP(P)                                                                                       \
+  b2l_launch(head_mix_group_kernel<T, P>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, (const T*)wide,        \
+             wide_row_stride, (const T*)mix, heads, kv_heads, per_call, vdim, items)
   B2L_DISPATCH_FLOAT(dtype, "head_mix", {
     if (vdim % 4 == 0 && wide_row_stride % 4 == 0 && row_aligned4<T>(out) && row_aligned4<T>(wide)) {
-      const unsigned grid = (unsigned)(cdiv64(total / 4, 256) < 148 * 16 ? cdiv64(total / 4, 256) : 148 * 16);
-      b2l_launch(head_mix_vec_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, (const T*)wide, wide_row_stride,
-                 (const T*)mix, heads, kv_heads, per_call, vdim, total / 4);
+      const int per = heads / kv_heads;
+      const int64_t items = (per == 2 || per == 4 || per == 8) ? total / 4 / per : total / 4;
+      const unsigned grid = (unsigned)(cdiv64(items, 256) < 148 * 16 ? cdiv64(items, 256) : 148 * 16);
+      if (per == 2) B2L_MIX_GROUP(2);
+      else if (per == 4) B2L_MIX_GROUP(4);
+      else if (per == 8) B2L_MIX_GROUP(8);
+      else
+        b2l_launch(head_mix_vec_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, (const T*)wide, wide_row_stride,
+                   (const T*)mix, heads, kv_heads, per_call, vdim, total / 4);
     } else {
       const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
       b2l_launch(head_mix_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, (const T*)wide, wide_row_stride,
                  (const T*)mix, heads, kv_heads, per_call, vdim, total);
     }
   });
+#undef B2L_MIX_GROUP
   B2L_LAUNCH_CHECK();
   return B2L_OK;
 }

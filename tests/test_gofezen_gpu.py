@@ -181,6 +181,8 @@ def _attention_weights(m, cols, talk, conv_w):
                                   dict(heads=8, kv_heads=4, dim=32, vdim=64, size=33, conv=2),     # two calls of two value heads
                                   dict(heads=2, kv_heads=2, dim=16, vdim=144, size=128, conv=4),   # one value head per call
                                   dict(heads=6, kv_heads=1, dim=8, vdim=8, size=1, conv=1),
+                                  dict(heads=8, kv_heads=2, dim=16, vdim=24, size=20, conv=2),     # four heads per kv head
+                                  dict(heads=8, kv_heads=1, dim=8, vdim=16, size=40, conv=1),      # eight
                                   dict(heads=2, kv_heads=1, dim=40, vdim=24, size=1000, conv=5)])
 def test_convolved_window_attention_with_mixed_heads_in_portions_and_single_tokens(dtype, tol, geom):
     m = O.left_entry(scale=2.0 / geom["dim"] ** 0.5, **geom)        # scores of a few units: a pointed softmax
